@@ -2,11 +2,12 @@ from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 from .lfm2 import ConfigError, Lfm2Config
 from .kemitar import KemitarConfig
 from .diforax import DiforaxConfig
+from .gukosun import GukosunConfig
 from .registry import (Architecture, UnknownArchitecture, architecture_name, architectures,
                        load_config, lookup, read_config_json, register_architecture)
 
 __all__ = [
-    "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "ConfigError", "Lfm2Config", "KemitarConfig", "DiforaxConfig",
+    "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "ConfigError", "Lfm2Config", "KemitarConfig", "DiforaxConfig", "GukosunConfig",
     "Architecture", "UnknownArchitecture", "architecture_name", "architectures", "load_config",
     "lookup", "read_config_json", "register_architecture",
 ]

@@ -88,6 +88,7 @@ class ModelSpec:
     embedding_scale: float = 1.0        # embedding rows are multiplied by this (LFM2: 1)
     embedding: Optional[PartSpec] = None  # None: the plain table lookup; else an embedding part
     logit_softcap: float = 0.0          # > 0: logits = cap * tanh(logits / cap) (LFM2: off)
+    logit_scale: float = 1.0            # logits are multiplied by this (in fp32, behind the head)
     # names a checkpoint of the architecture may carry that this configuration does not use (the
     # tensors of a sublayer some layer leaves out); the loader passes them over instead of refusing
     unused_tensors: Tuple[str, ...] = ()

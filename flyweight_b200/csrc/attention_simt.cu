@@ -28,12 +28,15 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pool,
                       const TC* __restrict__ v_pool, const int* __restrict__ positions,
                       const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                       int max_pages, int page_size, TO* __restrict__ out, int nh, int nkv, int hd,
-                      int window, float scale) {
+                      int window, float scale, const float* __restrict__ sink, float softcap) {
     fwb::pdl_entry();
     extern __shared__ float smem[];
     const int group = nh / nkv;
-    float* qs = smem;                         // [group][hd]
-    float* ks = qs + group * hd;              // [TILE][hd+1]
+    // a block takes up to WARPS * MAX_HPW query heads of its KV head; a larger group is cut over blockIdx.z
+    const int g0 = blockIdx.z * (WARPS * MAX_HPW);
+    const int mine = group - g0 < WARPS * MAX_HPW ? group - g0 : WARPS * MAX_HPW;
+    float* qs = smem;                         // [mine][hd]
+    float* ks = qs + mine * hd;               // [TILE][hd+1]
     float* vs = ks + TILE * (hd + 1);         // [TILE][hd]
     const int t = blockIdx.x, kvh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -41,17 +44,21 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pool,
     const int* table = block_table + (size_t)tok_seg[t] * max_pages;
     const int lo = fwb::first_visible_key(pos, window);
 
-    for (int i = threadIdx.x; i < group * hd; i += blockDim.x)
-        qs[i] = to_f32<TQ>(q[((size_t)t * nh + (size_t)kvh * group) * hd + i]);
+    for (int i = threadIdx.x; i < mine * hd; i += blockDim.x)
+        qs[i] = to_f32<TQ>(q[((size_t)t * nh + (size_t)kvh * group + g0) * hd + i]);
 
     float m[MAX_HPW], l[MAX_HPW], acc[MAX_HPW][MAX_DPL];
 #pragma unroll
     for (int a = 0; a < MAX_HPW; ++a) {
-        m[a] = -INFINITY;
-        l[a] = 0.0f;
+        // a sink: a key of score sink[head] (not scaled, not capped) whose value is zero starts the row
+        const int g = warp + a * WARPS;
+        const bool sunk = sink != nullptr && g < mine;
+        m[a] = sunk ? sink[kvh * group + g0 + g] : -INFINITY;
+        l[a] = sunk ? 1.0f : 0.0f;
 #pragma unroll
         for (int d = 0; d < MAX_DPL; ++d) acc[a][d] = 0.0f;
     }
+    const float inv_cap = softcap > 0.0f ? 1.0f / softcap : 0.0f;
 
     for (int base = (lo / TILE) * TILE; base <= pos; base += TILE) {
         __syncthreads();
@@ -70,12 +77,14 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pool,
 #pragma unroll
         for (int a = 0; a < MAX_HPW; ++a) {
             const int g = warp + a * WARPS;
-            if (g >= group) break;
+            if (g >= mine) break;
             const float* qh = qs + g * hd;
             const float* kr = ks + lane * (hd + 1);
             float s = 0.0f;
             for (int d = 0; d < hd; ++d) s = fmaf(qh[d], kr[d], s);
-            s = seen ? s * scale : -INFINITY;
+            s *= scale;
+            if (softcap > 0.0f) s = softcap * tanhf(s * inv_cap);
+            s = seen ? s : -INFINITY;
             const float tile_max = warp_max(s);
             if (tile_max == -INFINITY) continue;   // nothing visible in this tile (warp-uniform)
             const float m_new = fmaxf(m[a], tile_max);
@@ -98,9 +107,9 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pool,
 #pragma unroll
     for (int a = 0; a < MAX_HPW; ++a) {
         const int g = warp + a * WARPS;
-        if (g >= group) break;
+        if (g >= mine) break;
         const float inv = 1.0f / l[a];
-        TO* dst = out + ((size_t)t * nh + (size_t)kvh * group + g) * hd;
+        TO* dst = out + ((size_t)t * nh + (size_t)kvh * group + g0 + g) * hd;
 #pragma unroll
         for (int d = 0; d < MAX_DPL; ++d) {
             const int c = lane + 32 * d;
@@ -118,17 +127,27 @@ FWB_API int fwb_attention_simt(const void* q, int q_bf16, const void* k_pool, co
                                int cache_bf16, const int* positions, const int* tok_seg,
                                const int* block_table, int max_pages, int page_size, void* out,
                                int out_bf16, int T, int nh, int nkv, int hd, int window, float scale,
-                               cudaStream_t stream) {
+                               cudaStream_t stream);
+
+// The general form.  sink: fp32 [nh] or null -- a score per head (not scaled, not capped) that joins the
+// row's softmax denominator and has no value.  softcap > 0: score <- softcap * tanh(score / softcap)
+// behind the scale.
+FWB_API int fwb_attention_simt_sink(const void* q, int q_bf16, const void* k_pool, const void* v_pool,
+                                    int cache_bf16, const int* positions, const int* tok_seg,
+                                    const int* block_table, int max_pages, int page_size, void* out,
+                                    int out_bf16, int T, int nh, int nkv, int hd, int window, float scale,
+                                    const float* sink, float softcap, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!q || !k_pool || !v_pool || !positions || !tok_seg || !block_table || !out)
         return FWB_BAD_ARGUMENT;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || max_pages <= 0) return FWB_BAD_ARGUMENT;
     if (page_size <= 0 || page_size % TILE != 0) return FWB_UNSUPPORTED;
     const int group = nh / nkv;
-    if (group > WARPS * MAX_HPW || hd > 32 * MAX_DPL || nkv > 65535) return FWB_UNSUPPORTED;
-    const size_t smem = ((size_t)group * hd + (size_t)TILE * (2 * hd + 1)) * sizeof(float);
+    const int cuts = (group + WARPS * MAX_HPW - 1) / (WARPS * MAX_HPW);
+    if (hd > 32 * MAX_DPL || nkv > 65535 || cuts > 65535) return FWB_UNSUPPORTED;
+    const size_t smem = ((size_t)(cuts > 1 ? WARPS * MAX_HPW : group) * hd + (size_t)TILE * (2 * hd + 1)) * sizeof(float);
     using bf = __nv_bfloat16;
-    dim3 grid(T, nkv);
+    dim3 grid(T, nkv, cuts);
 #define FWB_ATTN(TQ, TC, TO)                                                                      \
     do {                                                                                          \
         auto kernel = attention_simt_kernel<TQ, TC, TO>;                                          \
@@ -140,11 +159,21 @@ FWB_API int fwb_attention_simt(const void* q, int q_bf16, const void* k_pool, co
         fwb::pdl(kernel, grid, WARPS * 32, smem, stream)((const TQ*)q, (const TC*)k_pool,               \
                                                    (const TC*)v_pool, positions, tok_seg,         \
                                                    block_table, max_pages, page_size, (TO*)out,   \
-                                                   nh, nkv, hd, window, scale);                   \
+                                                   nh, nkv, hd, window, scale, sink, softcap);    \
     } while (0)
     if (!q_bf16 && !cache_bf16 && !out_bf16) FWB_ATTN(float, float, float);
     else if (q_bf16 && cache_bf16 && out_bf16) FWB_ATTN(bf, bf, bf);
     else return FWB_UNSUPPORTED;
 #undef FWB_ATTN
     return fwb_launch_status();
+}
+
+FWB_API int fwb_attention_simt(const void* q, int q_bf16, const void* k_pool, const void* v_pool,
+                               int cache_bf16, const int* positions, const int* tok_seg,
+                               const int* block_table, int max_pages, int page_size, void* out,
+                               int out_bf16, int T, int nh, int nkv, int hd, int window, float scale,
+                               cudaStream_t stream) {
+    return fwb_attention_simt_sink(q, q_bf16, k_pool, v_pool, cache_bf16, positions, tok_seg, block_table,
+                                   max_pages, page_size, out, out_bf16, T, nh, nkv, hd, window, scale, nullptr,
+                                   0.0f, stream);
 }

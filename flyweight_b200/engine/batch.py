@@ -176,3 +176,6 @@ class StepContext:
     precision: object
     device: object
     bad_token_flag: Optional[torch.Tensor] = None
+    # what one layer of the step hands to a later one (values that later layers mix in), by name;
+    # it lives as long as the step
+    shared: dict = field(default_factory=dict)

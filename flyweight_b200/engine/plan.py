@@ -538,6 +538,8 @@ def build_plan(model, caches, max_tokens: int, max_rows: int, num_slots: int, n_
     builder = PlanBuilder(model.precision, model.device, spec.hidden_size, max_tokens, max_rows, num_slots,
                           bad_flag)
     try:
+        if spec.logit_scale != 1.0:
+            raise NotPlannable("scaled logits have no native plan form")
         embedder = getattr(model, "embedder", None)
         if embedder is None:
             builder.embed(model.embedding, spec.vocab_size, spec.embedding_scale)

@@ -172,12 +172,13 @@ def tensor_core_shape_ok(n_heads: int, n_kv: int, head_dim: int, page_size: int)
     return groups is not None and ops.attention_mma_shape_ok(n_heads, groups, head_dim, page_size)
 
 
-def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtype, sink=None):
+def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtype, sink=None, softcap=0.0):
     """Causal GQA of every token of the step over its request's pages.  ``window`` is the kernels' one
     mask parameter: > 0 a sliding window of that many positions, < 0 chunks of ``-window`` positions
     counted from position 0 (a query sees its own chunk up to itself), 0 every earlier key.  A cache with one pool
     (``v_pool`` None) holds rows that serve as keys and as values.  ``sink``: fp32 [n_heads], a score
-    per head that joins every softmax denominator (not scaled, no value)."""
+    per head that joins every softmax denominator (not scaled, no value).  ``softcap`` > 0: scores become
+    ``softcap * tanh(score / softcap)`` behind the scale (the sink is not capped)."""
     batch = ctx.batch
     k_pool = cache.k_pool
     v_pool = cache.v_pool if cache.v_pool is not None else k_pool
@@ -187,7 +188,7 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
     if sink is not None or n_kv != pool_heads:
         extra = {"sink": sink, "groups": n_kv}
     if (_use_mma and q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
-            and out_dtype == torch.bfloat16
+            and out_dtype == torch.bfloat16 and not softcap
             and ops.attention_mma_shape_ok(n_heads, n_kv, head_dim, page_size)):
         if batch.max_segment == 1 and not _force_tiled:
             splits, tiles_per_split, in_cluster = decode_splits(batch.n_tokens, n_kv, block_table.shape[1], head_dim)
@@ -224,8 +225,5 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
         return ops.attention_prefill_mma(q, k_pool, v_pool, batch.positions, batch.seg_start,
                                          tile_seg, tile_tok0, n_tiles, tokens_per_tile, block_table,
                                          n_heads, window, scale, out=out, **extra)
-    if sink is not None or cache.v_pool is None:
-        raise lib.KernelError("this attention shape has no tensor-core kernel, and the fp32 kernel takes "
-                              "neither a sink nor rows that are key and value at once")
     return ops.attention_simt(q, k_pool, v_pool, batch.positions, batch.tok_seg, block_table,
-                              n_heads, window, scale, out_dtype)
+                              n_heads, window, scale, out_dtype, sink=sink, softcap=softcap)

@@ -104,6 +104,13 @@ def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
     return logits
 
 
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """``x *= factor`` in place on fp32."""
+    check_tensor("scaled tensor", x, torch.float32)
+    lib.call("fwb_scale", ptr(x), c_longlong(x.numel()), c_float(factor), stream())
+    return x
+
+
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     if x.dtype == dtype:
         return x
@@ -297,8 +304,11 @@ def qk_norm_rope(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Opti
 
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                    positions: torch.Tensor, tok_seg: torch.Tensor, block_table: torch.Tensor,
-                   n_heads: int, window: int, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
-    """Causal GQA over the paged cache, SIMT fp32 arithmetic.  q: [T][nh*hd]."""
+                   n_heads: int, window: int, scale: float, out_dtype: torch.dtype,
+                   sink: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
+    """Causal GQA over the paged cache, SIMT fp32 arithmetic.  q: [T][nh*hd].  ``sink``: fp32 [nh], a
+    score per head that joins every softmax denominator (not scaled, not capped, without a value);
+    ``softcap`` > 0: scores become ``softcap * tanh(score / softcap)`` behind the scale."""
     check_tensor("q", q)
     check_tensor("k pool", k_pool)
     check_tensor("v pool", v_pool, k_pool.dtype, k_pool.shape)
@@ -309,10 +319,15 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     _i32("positions", positions, T)
     _i32("tok_seg", tok_seg, T)
     _i32("block table", block_table)
+    if sink is not None:
+        check_tensor("sink", sink, torch.float32, (n_heads,))
+    if softcap < 0:
+        raise KernelError("a soft-cap must not be negative")
     out = torch.empty((T, n_heads * head_dim), dtype=out_dtype, device=q.device)
-    lib.call("fwb_attention_simt", ptr(q), is_bf16(q), ptr(k_pool), ptr(v_pool), is_bf16(k_pool),
+    lib.call("fwb_attention_simt_sink", ptr(q), is_bf16(q), ptr(k_pool), ptr(v_pool), is_bf16(k_pool),
              ptr(positions), ptr(tok_seg), ptr(block_table), block_table.shape[1], page_size,
-             ptr(out), is_bf16(out), T, n_heads, n_kv, head_dim, window, c_float(scale), stream())
+             ptr(out), is_bf16(out), T, n_heads, n_kv, head_dim, window, c_float(scale), ptr(sink),
+             c_float(softcap), stream())
     return out
 
 

@@ -1,6 +1,7 @@
-from . import diforax, kemitar, lfm2  # noqa: F401  (register the architectures)
+from . import diforax, gukosun, kemitar, lfm2  # noqa: F401  (register the architectures)
 from .diforax import DiforaxForCausalLM
+from .gukosun import GukosunForCausalLM
 from .kemitar import KemitarForCausalLM
 from .lfm2 import Lfm2ForCausalLM
 
-__all__ = ["DiforaxForCausalLM", "KemitarForCausalLM", "Lfm2ForCausalLM"]
+__all__ = ["DiforaxForCausalLM", "GukosunForCausalLM", "KemitarForCausalLM", "Lfm2ForCausalLM"]

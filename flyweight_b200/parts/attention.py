@@ -30,7 +30,16 @@ class GQAttention(Mixer):
     the rotation, every head of q and k is brought to unit root mean square behind it, without a
     weight; no ``q_norm``/``k_norm`` tensors); ``value_dim`` (the size of a value head when it differs
     from ``head_dim``: the pools and kernels then run at the larger of the two, the smaller heads padded
-    with zero channels through zero rows and columns of the matrices)."""
+    with zero channels through zero rows and columns of the matrices); ``qk_norm`` ("head", the default:
+    one weight of ``head_dim`` entries shared by the heads, the mean over each head; "whole": the RMS norm
+    goes over all heads of q (and of k) at once, before they are split, with weights of the whole
+    projection's size); ``sink`` (True: tensor ``sink`` [heads], a score per head that joins every softmax
+    denominator without a value, neither scaled nor capped); ``softcap`` (> 0: score <- cap tanh(score /
+    cap) behind the scale); ``gate`` ("head": tensor ``g`` [heads][H], every head's output times
+    sigmoid(g h) of its head; "element": ``g`` [heads value_dim][H], channel by channel; both read the
+    mixer's input); ``value_mix`` ("source": this layer's values, as cached, are also handed on to later
+    layers of the step under ``value_mix_key``; "mixed": v <- (1 - lam) v + lam v_source with the
+    tensor ``vmix``, one number, before v is cached)."""
     graph_safe = True
     takes_deferred_norm = True
     adds_residual = True
@@ -60,12 +69,33 @@ class GQAttention(Mixer):
             raise ValueError("an attention mixer norms q and k in front of the rotation or behind it, not both")
         if self.value_dim != self.qk_dim or self.unit_rms_eps is not None or self.chunk:
             self.head_dim = -(-max(self.qk_dim, self.value_dim) // 16) * 16
-        if self.head_dim % 16:
-            raise ValueError(f"head size {self.head_dim}: the attention kernels take head sizes "
-                             "in steps of 16")
-        if self.head_dim != self.qk_dim and self.eps is not None:
-            raise ValueError("padded heads go with the unweighted q/k norm only")
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.qk_norm = str(p.get("qk_norm", "head"))
+        if self.qk_norm not in ("head", "whole"):
+            raise ValueError(f"unknown q/k norm {self.qk_norm!r}; known: head, whole")
+        if self.qk_norm == "whole" and self.eps is None:
+            raise ValueError("a q/k norm over the whole projection needs qk_norm_eps")
+        self.has_sink = bool(p.get("sink", False))
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        self.gate = p.get("gate")
+        if self.gate not in (None, "head", "element"):
+            raise ValueError(f"unknown output gate {self.gate!r}; known: head, element")
+        self.value_mix = p.get("value_mix")
+        if self.value_mix not in (None, "source", "mixed"):
+            raise ValueError(f"unknown value mixing role {self.value_mix!r}; known: source, mixed")
+        self.value_mix_key = str(p.get("value_mix_key", "values"))
+        if self.value_mix and self.shares_cache:
+            raise ValueError("a mixer that reads another's cache has no values of its own to mix")
+        if self.softcap < 0:
+            raise ValueError("softcap must not be negative")
+        if self.value_dim != self.qk_dim or self.qk_dim % 16:
+            self.head_dim = -(-max(self.qk_dim, self.value_dim) // 16) * 16
+        # the launches LFM2 makes: nothing of the above, so the fused decode kernel and the native plan apply
+        self._plain = not (self.has_sink or self.softcap or self.gate or self.value_mix
+                           or self.qk_norm == "whole" or (self.head_dim != self.qk_dim and self.eps is not None))
+        # q|k|v leave their product in fp32 when another kernel works on them before the head kernel
+        # reads them (a norm over the whole projection, values mixed in place): one rounding, not two
+        self._wide_qkv = self.qk_norm == "whole" or self.value_mix is not None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.w_gate = self.sink = self.vmix = None
 
     @property
     def _kv_in(self) -> int:
@@ -79,9 +109,16 @@ class GQAttention(Mixer):
             out[n["k"]] = TensorDecl((self.n_kv * hd, H))
             out[n["v"]] = TensorDecl((self.n_kv * self.value_dim, H))
         if self.eps is not None:
-            out[n["q_norm"]] = TensorDecl((hd,), "norm")
+            whole = self.qk_norm == "whole"
+            out[n["q_norm"]] = TensorDecl((self.n_heads * hd if whole else hd,), "norm")
             if not self.shares_cache:
-                out[n["k_norm"]] = TensorDecl((hd,), "norm")
+                out[n["k_norm"]] = TensorDecl((self.n_kv * hd if whole else hd,), "norm")
+        if self.has_sink:
+            out[n["sink"]] = TensorDecl((self.n_heads,), "bias")
+        if self.gate:
+            out[n["g"]] = TensorDecl((self.n_heads * (self.value_dim if self.gate == "element" else 1), H))
+        if self.value_mix == "mixed":
+            out[n["vmix"]] = TensorDecl((), "bias", also=((1,),))
         return out
 
     def bind(self, get, precision: Precision, device):
@@ -111,20 +148,41 @@ class GQAttention(Mixer):
             wide[:, :, :self.value_dim] = w_o.view(w_o.shape[0], self.n_heads, self.value_dim)
             w_o = wide.view(w_o.shape[0], self.n_heads * D)
         self.w_o = precision.matrix(w_o, device)
+        def channels_padded(vector, per_head):
+            """[heads * per_head] -> [heads * D]: zeros behind every head's own channels."""
+            if per_head == D:
+                return vector
+            wide = vector.new_zeros((vector.numel() // per_head, D))
+            wide[:, :per_head] = vector.view(-1, per_head)
+            return wide.reshape(-1)
+
         if self.eps is not None:
-            self.q_norm = precision.vector(get(n["q_norm"]), device)
+            self.q_norm = precision.vector(channels_padded(get(n["q_norm"]), self.qk_dim), device)
             if not self.shares_cache:
-                self.k_norm = precision.vector(get(n["k_norm"]), device)
+                self.k_norm = precision.vector(channels_padded(get(n["k_norm"]), self.qk_dim), device)
+        if self.has_sink:
+            self.sink = precision.vector(get(n["sink"]), device)
+        if self.gate:
+            w_gate = get(n["g"])
+            self.w_gate = precision.matrix(rows_padded(w_gate, self.value_dim) if self.gate == "element" else w_gate,
+                                           device)
+        if self.value_mix == "mixed":
+            self.vmix = precision.vector(get(n["vmix"]).reshape(1), device)
+
+    def _matrices(self):
+        return tuple(m for m in (self.w_qkv, self.w_o, self.w_gate) if m is not None)
 
     def weight_bytes(self):
-        return (self.w_qkv.numel() * self.w_qkv.element_size()
-                + self.w_o.numel() * self.w_o.element_size())
+        return sum(m.numel() * m.element_size() for m in self._matrices())
 
     def flops_per_token(self):
-        return 2.0 * (self.w_qkv.numel() + self.w_o.numel())
+        return 2.0 * sum(m.numel() for m in self._matrices())
 
     def context_flops(self, n_tokens):
         # QK^T and PV: 4 operations per (query, visible key, channel); half the pairs are masked
+        if self.window and n_tokens > self.window:
+            pairs = n_tokens * self.window - 0.5 * self.window * self.window
+            return 4.0 * pairs * self.n_heads * self.head_dim
         if self.chunk and n_tokens > self.chunk:
             whole, rest = divmod(n_tokens, self.chunk)
             return 2.0 * (whole * self.chunk * self.chunk + rest * rest) * self.n_heads * self.head_dim
@@ -137,7 +195,8 @@ class GQAttention(Mixer):
 
     def _encode_extra(self) -> dict:
         if self.unit_rms_eps is None:
-            return {}
+            # (heads padded with zero channels: the mean of a weighted head norm goes over the true size)
+            return {"norm_dim": self.qk_dim} if self.head_dim != self.qk_dim and self.eps is not None else {}
         return {"unit_rms_after": True, "norm_dim": self.qk_dim}
 
     def state_spec(self):
@@ -148,6 +207,8 @@ class GQAttention(Mixer):
 
     def forward(self, ctx, h, cache, residual=None):
         act = ctx.precision.act_dtype
+        if not self._plain:
+            return self._forward_general(ctx, h, cache, residual)
         # q|k|v in the activation dtype; the head norm and the rotation widen it to fp32
         qkv = ops.linear(h, self.w_qkv, act)
         block_table = ctx.batch.block_tables[cache.group]
@@ -170,9 +231,51 @@ class GQAttention(Mixer):
                                                 self.span, self.scale, act)
         return ops.linear_into_residual(out, self.w_o, residual)
 
+    def _forward_general(self, ctx, h, cache, residual=None):
+        """The mixer with any of: a norm over the whole projection, padded heads under a weighted norm,
+        mixed values, a sink, capped scores, an output gate."""
+        from ..kernels import attention as attention_kernels
+        from ..kernels import mixing
+        act = ctx.precision.act_dtype
+        if not isinstance(h, torch.Tensor):
+            h = h.materialize(act)
+        D = self.head_dim
+        qkv = ops.linear(h, self.w_qkv, torch.float32 if self._wide_qkv else act)
+        block_table = ctx.batch.block_tables[cache.group]
+        k_at, v_at = self.n_heads * D, (self.n_heads + self._kv_in) * D
+        whole = self.qk_norm == "whole"
+        if whole:
+            ranges = [(0, self.q_norm, self.n_heads * self.qk_dim, self.eps)]
+            if self._kv_in:
+                ranges.append((k_at, self.k_norm, self.n_kv * self.qk_dim, self.eps))
+            mixing.rmsnorm_ranges_(qkv, ranges)
+        if self.value_mix == "source":
+            first = torch.empty((qkv.shape[0], self.n_kv * D), dtype=qkv.dtype, device=qkv.device)
+            mixing.value_mix_(qkv, v_at, self.n_kv * D, first, None)
+            ctx.shared[self.value_mix_key] = first
+        elif self.value_mix == "mixed":
+            first = ctx.shared.get(self.value_mix_key)
+            if first is None or tuple(first.shape) != (qkv.shape[0], self.n_kv * D) or first.dtype != qkv.dtype:
+                raise ValueError(f"no values of this step under {self.value_mix_key!r} that fit "
+                                 f"{self.n_kv} value heads of {D}: the source layer runs first and has the same shape")
+            mixing.value_mix_(qkv, v_at, self.n_kv * D, first, self.vmix)
+        extra = self._encode_extra()
+        q = self.position.encode(ctx, qkv, n_heads=self.n_heads, n_kv_in=self._kv_in, head_dim=D,
+                                 q_norm=None if whole else self.q_norm, k_norm=None if whole else self.k_norm,
+                                 eps=None if whole else (self.eps if self.unit_rms_eps is None else self.unit_rms_eps),
+                                 cache=cache, block_table=block_table, **extra)
+        out = attention_kernels.paged_attention(ctx, q, cache, block_table, self.n_heads, self.span, self.scale,
+                                                act, sink=self.sink, softcap=self.softcap)
+        if self.gate:
+            mixing.sigmoid_gate_mul_(out, ops.linear(h, self.w_gate, act), self.n_heads, D)
+        return ops.linear_into_residual(out, self.w_o, residual)
+
     def plan(self, builder, norm, cache):
         """The same operations for the native step plan (``engine/plan.py``)."""
         from ..engine.plan import EPI_ACT, NotPlannable
+        if not self._plain:
+            raise NotPlannable("sinks, capped scores, gates, mixed values and norms over the whole projection "
+                               "have no native plan form")
         act = builder.act_dtype
         plan_position = getattr(self.position, "plan", None)
         if self.unit_rms_eps is not None:

@@ -264,6 +264,33 @@ class StreamShift(Part):
         raise NotImplementedError
 
 
+class SideInput(Part):
+    """Something a layer adds into the residual stream from the step's token ids, behind its sublayers."""
+
+    def forward(self, ctx, x):
+        """Adds into the fp32 stream ``x`` in place."""
+        raise NotImplementedError
+
+
+class ChannelScale(Part):
+    """One learned number per channel of the stream (a layer scale).  params: size.  tensors: weight."""
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(self.params["size"])
+        self.weight = None
+
+    def declare(self):
+        return {self.names["weight"]: TensorDecl((self.size,), "norm")}
+
+    def bind(self, get, precision: Precision, device):
+        self.weight = precision.vector(get(self.names["weight"]), device)
+
+    def weight_bytes(self):
+        return self.size * 4
+
+
 class Arrangement:
     """How a layer's parts are wired around the residual stream.  ``ROLES`` maps each role name
     the arrangement knows to the family its part is built from (``norm``, ``mixer``,
@@ -284,7 +311,7 @@ class Arrangement:
                              + (f"missing parts {missing}; " if missing else "")
                              + "it wires " + ", ".join(self.ROLES))
         builders = {"norm": build_norm, "mixer": build_mixer, "feed_forward": build_feed_forward,
-                    "shift": build_shift}
+                    "shift": build_shift, "side": build_side_input, "scale": build_scale}
         self._built = []
         for role, (family, _) in self.ROLES.items():
             part = builders[family](layer.parts[role]) if role in layer.parts else None
@@ -334,6 +361,8 @@ _POSITIONS: Dict[str, type] = {}
 _ARRANGEMENTS: Dict[str, type] = {}
 _EMBEDDINGS: Dict[str, type] = {}
 _SHIFTS: Dict[str, type] = {}
+_SIDE_INPUTS: Dict[str, type] = {}
+_SCALES: Dict[str, type] = {"channel_scale": ChannelScale}
 
 
 def _register(table: Dict[str, type], what: str):
@@ -353,6 +382,7 @@ register_position = _register(_POSITIONS, "position encoding")
 register_arrangement = _register(_ARRANGEMENTS, "arrangement")
 register_embedding = _register(_EMBEDDINGS, "embedding")
 register_shift = _register(_SHIFTS, "stream shift")
+register_side_input = _register(_SIDE_INPUTS, "side input")
 
 
 def _build(table: Dict[str, type], what: str, spec: PartSpec):
@@ -386,6 +416,14 @@ def build_embedding(spec: PartSpec) -> Embedding:
 
 def build_shift(spec: PartSpec) -> StreamShift:
     return _build(_SHIFTS, "stream shift", spec)
+
+
+def build_side_input(spec: PartSpec) -> SideInput:
+    return _build(_SIDE_INPUTS, "side input", spec)
+
+
+def build_scale(spec: PartSpec) -> ChannelScale:
+    return _build(_SCALES, "channel scale", spec)
 
 
 def build_arrangement(layer: LayerSpec) -> Arrangement:

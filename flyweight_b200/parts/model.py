@@ -143,6 +143,8 @@ class DecoderModel:
         if n is None:
             n = self.final_norm.forward(ctx, x, delta=pending, rows=batch.logit_rows)
         logits = ops.linear(n, self.head, torch.float32)
+        if self.spec.logit_scale != 1.0:
+            ops.scale_(logits, self.spec.logit_scale)
         if self.spec.logit_softcap > 0:
             ops.softcap_(logits, self.spec.logit_softcap)
         return logits

@@ -12,6 +12,8 @@ position 100 000 is as exact as at position 10 and every kernel reads the same v
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import PositionEncoding, register_position
@@ -19,7 +21,10 @@ from .base import PositionEncoding, register_position
 
 @register_position("rope")
 class Rope(PositionEncoding):
-    """params: theta, rotary_dim (even, <= head size), pairing ("half_split" | "interleaved")."""
+    """params: theta, rotary_dim (even, <= head size), pairing ("half_split" | "interleaved"), and
+    optionally ``scaling`` = {factor, low, high, original}: a frequency whose wavelength is shorter than
+    original/high stays, one whose wavelength is longer than original/low is divided by ``factor``, and in
+    between, with s = (original/wavelength - low) / (high - low), it becomes (1 - s) f/factor + s f."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -30,12 +35,31 @@ class Rope(PositionEncoding):
             raise ValueError("rotary_dim must be even")
         if self.pairing not in ("half_split", "interleaved"):
             raise ValueError(f"unknown rotary pairing {self.pairing!r}")
+        self.scaling = dict(self.params["scaling"]) if self.params.get("scaling") else None
+        if self.scaling is not None:
+            missing = [key for key in ("factor", "low", "high", "original") if self.scaling.get(key) is None]
+            if missing:
+                raise ValueError("rotary frequency scaling is missing " + ", ".join(missing))
+            if float(self.scaling["high"]) == float(self.scaling["low"]) or float(self.scaling["factor"]) <= 0:
+                raise ValueError("rotary frequency scaling needs high != low and a positive factor")
+
+    def frequencies(self) -> torch.Tensor:
+        """float64 [rotary_dim/2]: theta^(-2i/rotary_dim), scaled by wavelength when ``scaling`` is set."""
+        half = self.rotary_dim // 2
+        exponent = torch.arange(half, dtype=torch.float64) * (-2.0 / max(self.rotary_dim, 1))
+        freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), exponent)
+        if self.scaling is None:
+            return freq
+        factor, low, high = (float(self.scaling[key]) for key in ("factor", "low", "high"))
+        original = float(self.scaling["original"])
+        wave = 2.0 * math.pi / freq
+        blend = (original / wave - low) / (high - low)
+        mixed = (1.0 - blend) * freq / factor + blend * freq
+        return torch.where(wave < original / high, freq, torch.where(wave > original / low, freq / factor, mixed))
 
     def table(self, n_positions: int, device):
         """[n_positions][rotary_dim/2][2] fp32: (cos, sin) of every angle."""
-        half = self.rotary_dim // 2
-        exponent = torch.arange(half, dtype=torch.float64) * (-2.0 / max(self.rotary_dim, 1))
-        inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), exponent)
+        inv_freq = self.frequencies()
         angle = torch.arange(n_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
         table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).to(torch.float32)
         return table.contiguous().to(device)
