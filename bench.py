@@ -88,7 +88,34 @@ def diforax_like(lfm2: dict, ff: int) -> dict:
             "layers": layers}
 
 
-# Kemitar and Diforax beside LFM2 at equal layer sizes (--compare): the feed-forward widths are what
+def gukosun_like(lfm2: dict, ff: int) -> dict:
+    """A Gukosun configuration with the layer sizes of an LFM2 one (width, depth, vocabulary, query and
+    key/value heads of 64): where LFM2 attends, a layer whose mixer is an attention over every earlier
+    key (rotated, scores capped at 30, a sink, a gate per head) beside a decayed linear attention
+    (width / 128 heads of 128 x 128 state); everywhere else a sliding window of 1,024 keys with a sink,
+    values mixed with the first such layer's and a gate per channel.  Every layer has the dense
+    feed-forward of LFM2's width and a token side input of 64 entries."""
+    width, heads, kv = lfm2["hidden_size"], lfm2["num_attention_heads"], lfm2["num_key_value_heads"]
+    linear_heads = width // 128
+    decay = [round(1.0 - 2.0 ** (-3.0 - 5.0 * h / max(linear_heads - 1, 1)), 6) for h in range(linear_heads)]
+    layers = []
+    for index in range(lfm2["num_hidden_layers"]):
+        if index in lfm2["full_attn_idxs"]:
+            left = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "scale": 0.125, "softcap": 30.0,
+                    "rot": {"base": 1000000.0, "dims": 64,
+                            "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            right = {"heads": linear_heads, "dim": 128, "vdim": 128, "decay": decay}
+            layers.append({"type": "parallel", "mixer": {"left": left, "right": right},
+                           "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            mixer = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "scale": 0.125,
+                     "mask": {"size": 1024}, "v_mix": True}
+            layers.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Gukosun", "vocab": lfm2["vocab_size"], "width": width, "norm": {"eps": 1e-5},
+            "logit_scale": 0.5, "token_side": {"dim": 64}, "layers": layers}
+
+
+# Kemitar, Diforax and Gukosun beside LFM2 at equal layer sizes (--compare): the feed-forward widths are what
 # LFM2's rule makes of ``intermediate_size`` at these sizes.
 KEMITAR = {"kemitar-350m": ("lfm2-350m", 4608), "kemitar-1.2b": ("lfm2-1.2b", 8192)}
 for _name, (_twin, _ff) in KEMITAR.items():
@@ -96,7 +123,10 @@ for _name, (_twin, _ff) in KEMITAR.items():
 DIFORAX = {"diforax-350m": ("lfm2-350m", 4608), "diforax-1.2b": ("lfm2-1.2b", 8192)}
 for _name, (_twin, _ff) in DIFORAX.items():
     MODELS[_name] = diforax_like(MODELS[_twin], _ff)
-COMPARE = {**KEMITAR, **DIFORAX}
+GUKOSUN = {"gukosun-350m": ("lfm2-350m", 4608), "gukosun-1.2b": ("lfm2-1.2b", 8192)}
+for _name, (_twin, _ff) in GUKOSUN.items():
+    MODELS[_name] = gukosun_like(MODELS[_twin], _ff)
+COMPARE = {**KEMITAR, **DIFORAX, **GUKOSUN}
 
 
 def vocab_of(config: dict) -> int:
@@ -218,6 +248,21 @@ def kv_bytes_per_token(model) -> int:
             if member is not None and hasattr(member, "n_kv_heads"):
                 pools = 2 if getattr(member, "values", True) else 1
                 total += pools * member.n_kv_heads * member.head_dim * model.precision.cache_dtype.itemsize
+    return total
+
+
+def cache_bytes_read(model, context: int) -> int:
+    """Bytes of cached keys and values one decoded token at ``context`` reads: per layer the positions
+    its mask lets it see (a sliding window cuts them; a chunked mask through ``context_seen``)."""
+    total = 0
+    seen = min(context, context_seen(model, context))
+    for entry in model.spec.schedule:
+        spec = model.layers[entry.layer].state_spec() if entry.cache_of is None else None
+        for member in (spec if isinstance(spec, tuple) else (spec,)):
+            if member is not None and hasattr(member, "n_kv_heads"):
+                pools = 2 if getattr(member, "values", True) else 1
+                positions = min(seen, member.window) if member.window else seen
+                total += positions * pools * member.n_kv_heads * member.head_dim * model.precision.cache_dtype.itemsize
     return total
 
 
@@ -474,7 +519,7 @@ def run_sizes(args) -> int:
 
 
 def run_compare(args) -> int:
-    """``--compare kemitar-350m|kemitar-1.2b|diforax-350m|diforax-1.2b``: the model with random weights beside LFM2 at equal layer
+    """``--compare kemitar-350m|kemitar-1.2b|diforax-350m|diforax-1.2b|gukosun-350m|gukosun-1.2b``: the model with random weights beside LFM2 at equal layer
     sizes, both through the same step function -- prompts of 512, 2,048 and 8,192 tokens in one step
     (tokens/s and TFLOP/s of the model's own flop count) and decode steps at batch 1, 8 and 64 over 4,096
     cached tokens (tokens/s, and the bytes a step must read against the measured copy bandwidth).  One
@@ -509,7 +554,7 @@ def run_compare(args) -> int:
             # what a step must move: the weights it touches (of routed experts: those its tokens can
             # choose), every request's cached keys and values, and its fixed-size state in and out
             step_bytes = (model.weight_bytes(with_embedding_rows=batch, tokens=batch)
-                          + batch * min(CONTEXT, context_seen(model, CONTEXT)) * kv_bytes_per_token(model)
+                          + batch * cache_bytes_read(model, CONTEXT)
                           + 2 * batch * state_bytes_per_request(model))
             line["decode"][f"b{batch}"] = {
                 "ms_per_step": round(timed["ms_per_step"], 4), "tokens_per_s": round(timed["tokens_per_s"]),
@@ -803,7 +848,7 @@ def main() -> int:
                         help="64 requests, prompts of 128 to 8,192 tokens in portions of 512 beside decoding "
                              "requests, 256 new tokens each, through the public runtime (e.g. lfm2-350m)")
     parser.add_argument("--compare", default=None, metavar="MODEL",
-                        help="kemitar-350m, kemitar-1.2b, diforax-350m or diforax-1.2b beside LFM2 at equal layer sizes: prompts and decode steps")
+                        help="kemitar-350m, kemitar-1.2b, diforax-350m, diforax-1.2b, gukosun-350m or gukosun-1.2b beside LFM2 at equal layer sizes: prompts and decode steps")
     parser.add_argument("--kernel-times", default=None, metavar="[MODEL:]decode[@BATCHxCONTEXT]|prefill|TOKENS",
                         help="one step with CUDA events around every launch: time per kernel as JSON")
     args = parser.parse_args()

@@ -169,8 +169,10 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&p)[
 template <int HD, int NT>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD / 8][4], float (&m)[2],
                                                float (&l)[2], int key_base, const int (&lo)[2],
-                                               const int (&hi)[2], float scale, int lane) {
+                                               const int (&hi)[2], float scale, float softcap, int lane) {
     const int t = lane & 3;
+    // capped scores: cap * tanh(score / cap), in base 2 like the scale (which has log2(e) folded in)
+    const float cap_pre = softcap > 0.0f ? scale / (softcap * LOG2E) : 0.0f, cap_post = softcap * LOG2E;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < NT; ++n)
@@ -178,7 +180,8 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[HD 
         for (int j = 0; j < 4; ++j) {
             const int key = key_base + n * 8 + 2 * t + (j & 1);
             const int h = j >> 1;
-            const float v = (key >= lo[h] && key <= hi[h]) ? s[n][j] * scale : -INFINITY;   // scale has log2(e) folded in
+            const float capped = softcap > 0.0f ? cap_post * fwb::tanh_fast_f32(s[n][j] * cap_pre) : s[n][j] * scale;
+            const float v = (key >= lo[h] && key <= hi[h]) ? capped : -INFINITY;   // scale has log2(e) folded in
             s[n][j] = v;
             mx[h] = fmaxf(mx[h], v);
         }
@@ -244,7 +247,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ tile_tok0, const int* __restrict__ block_table,
                          int max_pages, __nv_bfloat16* __restrict__ out, int nh, int nkv, int group,
                          int tokens_per_tile, int window, float scale, const float* __restrict__ sink,
-                         int pool_nkv) {
+                         int pool_nkv, float softcap) {
     fwb::pdl_entry();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -329,7 +332,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         if (warp_hi >= tile * KEYS) {
             float sc[8][4];
             qk_tile<HD, 8>(sc, qf, stage_k(s), 0, lane);
-            softmax_update<HD, 8>(sc, o, m, l, tile * KEYS, lo, hi, scale, lane);
+            softmax_update<HD, 8>(sc, o, m, l, tile * KEYS, lo, hi, scale, softcap, lane);
             pv_tile<HD, 8>(o, sc, stage_v(s), 0, lane);
         }
         __syncthreads();                                    // the stage may be overwritten next
@@ -351,6 +354,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 struct FusedQkv {
     const float* sink;           // [nh] or null: a score per head that joins the softmax denominator (no value)
     int pool_nkv;                // heads of the pools; 0: nkv (else several groups of query heads share a pool head)
+    float softcap;               // > 0: score <- softcap * tanh(score / softcap) behind the scale
     const __nv_bfloat16* qkv;    // [T][(nh + 2 nkv_in) HD]; null: `q` holds finished queries
     const float* wq;             // [HD] head-norm weights (unused when !use_norm)
     const float* wk;
@@ -560,7 +564,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         float sc[2][4];                                     // this warp's 16 keys of the tile
         qk_tile<HD, 2, TMA>(sc, qf, stage_k(s), warp * 16, lane);
-        softmax_update<HD, 2>(sc, o, m, l, tile * KEYS + warp * 16, lo, hi, scale, lane);
+        softmax_update<HD, 2>(sc, o, m, l, tile * KEYS + warp * 16, lo, hi, scale, fused.softcap, lane);
         pv_tile<HD, 2, TMA>(o, sc, stage_v(s), warp * 16, lane);
         __syncthreads();
     }
@@ -712,7 +716,7 @@ template <int HD>
 int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const int* positions,
                    const int* seg_start, const int* tile_seg, const int* tile_tok0, const int* block_table,
                    int max_pages, void* out, int n_tiles, int nh, int nkv, int tokens_per_tile, int window,
-                   float scale, const float* sink, int pool_nkv, cudaStream_t stream) {
+                   float scale, const float* sink, int pool_nkv, float softcap, cudaStream_t stream) {
     auto kernel = attention_prefill_kernel<HD>;
     int st = opt_in_smem(kernel, Smem<HD>::BYTES);
     if (st != FWB_OK) return st;
@@ -720,7 +724,7 @@ int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const 
     fwb::pdl(kernel, dim3(n_tiles, nkv), WARPS * 32, Smem<HD>::BYTES, stream)(
         (const bf*)q, (const bf*)k_pool, (const bf*)v_pool, positions, seg_start, tile_seg, tile_tok0,
         block_table, max_pages, (bf*)out, nh, nkv, nh / nkv, tokens_per_tile, window, scale * LOG2E, sink,
-        pool_nkv > 0 ? pool_nkv : nkv);
+        pool_nkv > 0 ? pool_nkv : nkv, softcap);
     return fwb_launch_status();
 }
 
@@ -859,13 +863,15 @@ bool shape_ok(int nh, int nkv, int hd, int page_size) {
 // softmax denominator and has no value.  pool_nkv: heads the pools have (0: nkv); with fewer than
 // nkv, nkv counts groups of nh / nkv query heads and group i reads pool head i * pool_nkv / nkv
 // (one latent row per token shared by every head: pool_nkv = 1).  v_pool may be k_pool.
-FWB_API int fwb_attention_prefill_mma_sink(const void* q, const void* k_pool, const void* v_pool,
-                                           const int* positions, const int* seg_start, const int* tile_seg,
-                                           const int* tile_tok0, const int* block_table, int max_pages,
-                                           int page_size, void* out, int n_tiles, int nh, int nkv, int hd,
-                                           int tokens_per_tile, int window, float scale, const float* sink,
-                                           int pool_nkv, cudaStream_t stream) {
+// softcap > 0: score <- softcap * tanh(score / softcap) behind the scale (the sink is not capped).
+FWB_API int fwb_attention_prefill_mma_capped(const void* q, const void* k_pool, const void* v_pool,
+                                             const int* positions, const int* seg_start, const int* tile_seg,
+                                             const int* tile_tok0, const int* block_table, int max_pages,
+                                             int page_size, void* out, int n_tiles, int nh, int nkv, int hd,
+                                             int tokens_per_tile, int window, float scale, const float* sink,
+                                             int pool_nkv, float softcap, cudaStream_t stream) {
     if (n_tiles <= 0) return FWB_OK;
+    if (!(softcap >= 0.0f)) return FWB_BAD_ARGUMENT;
     if (!q || !k_pool || !v_pool || !positions || !seg_start || !tile_seg || !tile_tok0 || !block_table || !out)
         return FWB_BAD_ARGUMENT;
     if (!shape_ok(nh, nkv, hd, page_size)) return FWB_UNSUPPORTED;
@@ -873,9 +879,20 @@ FWB_API int fwb_attention_prefill_mma_sink(const void* q, const void* k_pool, co
     if (tokens_per_tile < 1 || tokens_per_tile * (nh / nkv) > 64) return FWB_BAD_ARGUMENT;
 #define CALL(HD)                                                                                          \
     launch_prefill<HD>(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, block_table, max_pages, \
-                       out, n_tiles, nh, nkv, tokens_per_tile, window, scale, sink, pool_nkv, stream)
+                       out, n_tiles, nh, nkv, tokens_per_tile, window, scale, sink, pool_nkv, softcap, stream)
     FWB_HD_SWITCH(hd, CALL)
 #undef CALL
+}
+
+FWB_API int fwb_attention_prefill_mma_sink(const void* q, const void* k_pool, const void* v_pool,
+                                           const int* positions, const int* seg_start, const int* tile_seg,
+                                           const int* tile_tok0, const int* block_table, int max_pages,
+                                           int page_size, void* out, int n_tiles, int nh, int nkv, int hd,
+                                           int tokens_per_tile, int window, float scale, const float* sink,
+                                           int pool_nkv, cudaStream_t stream) {
+    return fwb_attention_prefill_mma_capped(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, block_table,
+                                            max_pages, page_size, out, n_tiles, nh, nkv, hd, tokens_per_tile, window,
+                                            scale, sink, pool_nkv, 0.0f, stream);
 }
 
 FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const void* v_pool,
@@ -890,7 +907,7 @@ FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const v
     if (tokens_per_tile < 1 || tokens_per_tile * (nh / nkv) > 64) return FWB_BAD_ARGUMENT;
 #define CALL(HD)                                                                                          \
     launch_prefill<HD>(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, block_table, max_pages, \
-                       out, n_tiles, nh, nkv, tokens_per_tile, window, scale, nullptr, 0, stream)
+                       out, n_tiles, nh, nkv, tokens_per_tile, window, scale, nullptr, 0, 0.0f, stream)
     FWB_HD_SWITCH(hd, CALL)
 #undef CALL
 }
@@ -900,13 +917,14 @@ FWB_API int fwb_attention_prefill_mma(const void* q, const void* k_pool, const v
 // while the launch has few CTAs) or by a second kernel through scratch: part_o needs
 // T*nkv*splits*group*hd floats and part_ml T*nkv*splits*group*2 floats.  num_pages: the pools'
 // first extent (0: unknown, no TMA).
-FWB_API int fwb_attention_decode_mma_sink(const void* q, const void* k_pool, const void* v_pool,
-                                          const int* positions, const int* tok_seg, const int* block_table,
-                                          int max_pages, int page_size, int num_pages, void* out, float* part_o,
-                                          float* part_ml, int T, int nh, int nkv, int hd, int splits,
-                                          int tiles_per_split, int window, float scale, int merge_in_cluster,
-                                          const float* sink, int pool_nkv, cudaStream_t stream) {
+FWB_API int fwb_attention_decode_mma_capped(const void* q, const void* k_pool, const void* v_pool,
+                                            const int* positions, const int* tok_seg, const int* block_table,
+                                            int max_pages, int page_size, int num_pages, void* out, float* part_o,
+                                            float* part_ml, int T, int nh, int nkv, int hd, int splits,
+                                            int tiles_per_split, int window, float scale, int merge_in_cluster,
+                                            const float* sink, int pool_nkv, float softcap, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
+    if (!(softcap >= 0.0f)) return FWB_BAD_ARGUMENT;
     if (!q || !k_pool || !v_pool || !positions || !tok_seg || !block_table || !out) return FWB_BAD_ARGUMENT;
     if (!shape_ok(nh, nkv, hd, page_size) || T > 65535) return FWB_UNSUPPORTED;
     if (pool_nkv < 0 || pool_nkv > nkv || (pool_nkv > 0 && nkv % pool_nkv)) return FWB_BAD_ARGUMENT;
@@ -916,11 +934,24 @@ FWB_API int fwb_attention_decode_mma_sink(const void* q, const void* k_pool, con
     memset(&fused, 0, sizeof(fused));
     fused.sink = sink;
     fused.pool_nkv = pool_nkv;
+    fused.softcap = softcap;
 #define CALL(HD)                                                                                          \
     launch_decode<HD>(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, num_pages, out, part_o,  \
                       part_ml, T, nh, nkv, splits, tiles_per_split, window, scale, in_cluster, fused, stream)
     FWB_HD_SWITCH(hd, CALL)
 #undef CALL
+}
+
+// The same without capped scores.
+FWB_API int fwb_attention_decode_mma_sink(const void* q, const void* k_pool, const void* v_pool,
+                                          const int* positions, const int* tok_seg, const int* block_table,
+                                          int max_pages, int page_size, int num_pages, void* out, float* part_o,
+                                          float* part_ml, int T, int nh, int nkv, int hd, int splits,
+                                          int tiles_per_split, int window, float scale, int merge_in_cluster,
+                                          const float* sink, int pool_nkv, cudaStream_t stream) {
+    return fwb_attention_decode_mma_capped(q, k_pool, v_pool, positions, tok_seg, block_table, max_pages, page_size,
+                                           num_pages, out, part_o, part_ml, T, nh, nkv, hd, splits, tiles_per_split,
+                                           window, scale, merge_in_cluster, sink, pool_nkv, 0.0f, stream);
 }
 
 FWB_API int fwb_attention_decode_mma(const void* q, const void* k_pool, const void* v_pool,

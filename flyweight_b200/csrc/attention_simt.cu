@@ -19,7 +19,7 @@ namespace {
 
 constexpr int WARPS = 4;
 constexpr int TILE = 32;
-constexpr int MAX_HPW = 4;   // query heads per warp  -> group size <= 16
+constexpr int MAX_HPW = 4;   // query heads per warp  -> 16 heads of a group per block (larger groups: more blocks)
 constexpr int MAX_DPL = 8;   // head channels per lane -> head size <= 256
 
 template <typename TQ, typename TC, typename TO>

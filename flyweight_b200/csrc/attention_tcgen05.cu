@@ -79,6 +79,8 @@ struct AttnParams {
     int items_per_cta;           // 2: CTA c takes items c and n-1-c; 1: one item each (few items)
     float scale_log2;            // softmax scale * log2(e)
     const float* sink;           // [nh] or null: a score per head (not scaled) in the softmax denominator, no value
+    float cap_pre, cap_unit;     // capped scores: raw <- cap_unit * tanh(raw * cap_pre), cap_pre = scale / cap,
+                                 // cap_unit = cap / scale, so that the scale that follows gives cap * tanh(score / cap); 0: off
     int* status;
 };
 
@@ -330,6 +332,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
                 float sc[KEYS];
                 tmem_ld64(lane_addr + buf * KEYS, sc);
                 tc_fence_before();                         // S is out of its buffer before this warp says that P is ready
+                if (prm.cap_pre != 0.0f) {
+#pragma unroll
+                    for (int i = 0; i < KEYS; ++i) sc[i] = prm.cap_unit * fwb::tanh_fast_f32(sc[i] * prm.cap_pre);
+                }
                 // a tile every row sees whole needs no mask (rows without a token are never stored)
                 const bool whole = key0 >= lo_max && key0 + KEYS - 1 <= item.pos_first;
                 if (!whole) {
@@ -487,13 +493,35 @@ FWB_API int fwb_attention_prefill_tcgen05(const void* q, const void* k_pool, con
 
 // The same with a sink: fp32 [nh] or null, a score per head that joins every row's softmax denominator
 // (not scaled, no value).  v_pool may be k_pool (a row that serves as key and as value).
+FWB_API int fwb_attention_prefill_tcgen05_capped(const void* q, const void* k_pool, const void* v_pool,
+                                                 const int* positions, const int* seg_start, const int* tile_seg,
+                                                 const int* tile_tok0, const int* block_table, int max_pages,
+                                                 int page_size, int num_pages, void* out, int n_tiles, int nh,
+                                                 int nkv, int hd, int tokens_per_tile, int window, float scale,
+                                                 const float* sink, float softcap, cudaStream_t stream);
+
 FWB_API int fwb_attention_prefill_tcgen05_sink(const void* q, const void* k_pool, const void* v_pool,
                                                const int* positions, const int* seg_start, const int* tile_seg,
                                                const int* tile_tok0, const int* block_table, int max_pages,
                                                int page_size, int num_pages, void* out, int n_tiles, int nh,
                                                int nkv, int hd, int tokens_per_tile, int window, float scale,
                                                const float* sink, cudaStream_t stream) {
+    return fwb_attention_prefill_tcgen05_capped(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0,
+                                                block_table, max_pages, page_size, num_pages, out, n_tiles, nh, nkv,
+                                                hd, tokens_per_tile, window, scale, sink, 0.0f, stream);
+}
+
+// The general form.  softcap > 0: score <- softcap * tanh(score / softcap) behind the scale (the sink is
+// not capped); a scale of 0 with a cap is refused (every score would be 0: not worth a form of its own).
+FWB_API int fwb_attention_prefill_tcgen05_capped(const void* q, const void* k_pool, const void* v_pool,
+                                                 const int* positions, const int* seg_start, const int* tile_seg,
+                                                 const int* tile_tok0, const int* block_table, int max_pages,
+                                                 int page_size, int num_pages, void* out, int n_tiles, int nh,
+                                                 int nkv, int hd, int tokens_per_tile, int window, float scale,
+                                                 const float* sink, float softcap, cudaStream_t stream) {
     if (n_tiles <= 0) return FWB_OK;
+    if (!(softcap >= 0.0f)) return FWB_BAD_ARGUMENT;
+    if (softcap > 0.0f && scale == 0.0f) return FWB_UNSUPPORTED;
     if (!q || !k_pool || !v_pool || !positions || !seg_start || !tile_seg || !tile_tok0 || !block_table || !out)
         return FWB_BAD_ARGUMENT;
     if (!fwb_attention_prefill_tcgen05_accepts(nh, nkv, hd, page_size)) return FWB_UNSUPPORTED;
@@ -525,6 +553,8 @@ FWB_API int fwb_attention_prefill_tcgen05_sink(const void* q, const void* k_pool
     prm.items_per_cta = (long)n_tiles * nkv <= 148 ? 1 : 2;
     prm.scale_log2 = scale * LOG2E;
     prm.sink = sink;
+    prm.cap_pre = softcap > 0.0f ? scale / softcap : 0.0f;
+    prm.cap_unit = softcap > 0.0f ? softcap / scale : 0.0f;
     prm.status = status_word();
     return hd == 64 ? launch<64>(map_k, map_v, prm, n_tiles, stream)
                     : launch<128>(map_k, map_v, prm, n_tiles, stream);

@@ -129,6 +129,13 @@ __device__ __forceinline__ float gelu_tanh_f32(float g) {
 }
 
 // silu(g) = g * sigmoid(g), sigmoid split by sign so neither branch overflows.
+// tanh with an absolute error of a few 1e-8 from one fast exponential: (1 - e) / (1 + e), e = exp(-2|x|)
+// (for the capped scores of the tensor-core attention kernels; the fp32 kernels call tanhf)
+__device__ __forceinline__ float tanh_fast_f32(float x) {
+    const float e = __expf(-2.0f * fabsf(x));
+    return copysignf(__fdividef(1.0f - e, 1.0f + e), x);
+}
+
 __device__ __forceinline__ float silu_f32(float g) {
     const float e = expf(-fabsf(g));
     const float sig = g >= 0.0f ? 1.0f / (1.0f + e) : e / (1.0f + e);

@@ -187,8 +187,10 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
     extra = {}
     if sink is not None or n_kv != pool_heads:
         extra = {"sink": sink, "groups": n_kv}
+    capped = {"softcap": float(softcap)} if softcap else {}
+    extra.update(capped)
     if (_use_mma and q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
-            and out_dtype == torch.bfloat16 and not softcap
+            and out_dtype == torch.bfloat16
             and ops.attention_mma_shape_ok(n_heads, n_kv, head_dim, page_size)):
         if batch.max_segment == 1 and not _force_tiled:
             splits, tiles_per_split, in_cluster = decode_splits(batch.n_tokens, n_kv, block_table.shape[1], head_dim)
@@ -219,7 +221,7 @@ def paged_attention(ctx, q, cache, block_table, n_heads, window, scale, out_dtyp
             return ops.attention_prefill_tcgen05(q, k_pool, v_pool, batch.positions, batch.seg_start,
                                                  tile_seg, tile_tok0, n_tiles, tokens_per_tile,
                                                  block_table, n_heads, window, scale, out=out,
-                                                 **({"sink": sink} if sink is not None else {}))
+                                                 **({"sink": sink} if sink is not None else {}), **capped)
         tokens_per_tile = max(1, 64 // group)
         tile_seg, tile_tok0, n_tiles = batch.attention_tiles(tokens_per_tile, first)
         return ops.attention_prefill_mma(q, k_pool, v_pool, batch.positions, batch.seg_start,

@@ -352,10 +352,11 @@ def _sink_and_groups(sink, groups, n_heads: int, n_kv: int):
 
 def attention_prefill_mma(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, n_tiles,
                           tokens_per_tile, block_table, n_heads, window, scale, out=None,
-                          sink=None, groups=None) -> torch.Tensor:
+                          sink=None, groups=None, softcap: float = 0.0) -> torch.Tensor:
     """Causal GQA of prompt portions (any mix of segments) on tensor cores; all bf16.  Only the
     rows of the given tiles are written (``out``: a tensor like q that other rows already live in).
-    ``v_pool`` may be ``k_pool`` itself; ``sink``, ``groups``: see ``_sink_and_groups``."""
+    ``v_pool`` may be ``k_pool`` itself; ``sink``, ``groups``: see ``_sink_and_groups``; ``softcap`` > 0:
+    scores become ``softcap * tanh(score / softcap)`` behind the scale."""
     check_tensor("q", q, torch.bfloat16)
     check_tensor("k pool", k_pool, torch.bfloat16)
     check_tensor("v pool", v_pool, torch.bfloat16, k_pool.shape)
@@ -373,10 +374,10 @@ def attention_prefill_mma(q, k_pool, v_pool, positions, seg_start, tile_seg, til
     else:
         check_tensor("attention output", out, torch.bfloat16, q.shape)
     groups = _sink_and_groups(sink, groups, n_heads, n_kv)
-    lib.call("fwb_attention_prefill_mma_sink", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
+    lib.call("fwb_attention_prefill_mma_capped", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
              ptr(seg_start), ptr(tile_seg), ptr(tile_tok0), ptr(block_table), block_table.shape[1],
              page_size, ptr(out), n_tiles, n_heads, groups, head_dim, tokens_per_tile, window,
-             c_float(scale), ptr(sink), n_kv, stream())
+             c_float(scale), ptr(sink), n_kv, c_float(softcap), stream())
     return out
 
 
@@ -388,7 +389,7 @@ def attention_tcgen05_shape_ok(n_heads: int, n_kv: int, head_dim: int, page_size
 
 def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg, tile_tok0, n_tiles,
                               tokens_per_tile, block_table, n_heads, window, scale, out=None,
-                              sink=None) -> torch.Tensor:
+                              sink=None, softcap: float = 0.0) -> torch.Tensor:
     """The same operation on tcgen05 tensor cores: 128 query rows per CTA, S and PV in tensor
     memory (head sizes 64 and 128); all bf16."""
     check_tensor("q", q, torch.bfloat16)
@@ -408,10 +409,10 @@ def attention_prefill_tcgen05(q, k_pool, v_pool, positions, seg_start, tile_seg,
     else:
         check_tensor("attention output", out, torch.bfloat16, q.shape)
     _sink_and_groups(sink, None, n_heads, n_kv)
-    lib.call("fwb_attention_prefill_tcgen05_sink", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
+    lib.call("fwb_attention_prefill_tcgen05_capped", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
              ptr(seg_start), ptr(tile_seg), ptr(tile_tok0), ptr(block_table), block_table.shape[1],
              page_size, num_pages, ptr(out), n_tiles, n_heads, n_kv, head_dim, tokens_per_tile, window,
-             c_float(scale), ptr(sink), stream())
+             c_float(scale), ptr(sink), c_float(softcap), stream())
     return out
 
 
@@ -467,7 +468,7 @@ def set_decode_attention_tma(on: bool, stages: int = 0) -> None:
 
 def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_heads, window, scale,
                          splits: int, tiles_per_split: int, merge_in_cluster: bool = False,
-                         out=None, n_tokens=None, sink=None, groups=None) -> torch.Tensor:
+                         out=None, n_tokens=None, sink=None, groups=None, softcap: float = 0.0) -> torch.Tensor:
     """Causal GQA of single decode tokens on tensor cores, the context cut into ``splits``
     slices of ``tiles_per_split`` 64-key tiles that run as separate CTAs and are merged: inside
     the kernel (``merge_in_cluster``, up to 8 slices as a thread-block cluster) or through scratch
@@ -496,9 +497,9 @@ def attention_decode_mma(q, k_pool, v_pool, positions, tok_seg, block_table, n_h
         group = n_heads // groups
         part_o = torch.empty((T, groups, splits, group, head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((T, groups, splits, group, 2), dtype=torch.float32, device=q.device)
-    lib.call("fwb_attention_decode_mma_sink", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
+    lib.call("fwb_attention_decode_mma_capped", ptr(q), ptr(k_pool), ptr(v_pool), ptr(positions),
              ptr(tok_seg), ptr(block_table), block_table.shape[1], page_size, k_pool.shape[0], ptr(out), ptr(part_o),
              ptr(part_ml), T, n_heads, groups, head_dim, splits, tiles_per_split, window,
-             c_float(scale), 1 if in_cluster else 0, ptr(sink), n_kv, stream(),
+             c_float(scale), 1 if in_cluster else 0, ptr(sink), n_kv, c_float(softcap), stream(),
              launches=2 if (splits > 1 and not in_cluster) else 1)
     return out

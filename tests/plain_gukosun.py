@@ -9,11 +9,40 @@ of matrix products, cached keys and values); the identity by default.
 """
 from __future__ import annotations
 
+import json
 import math
+import struct
+from pathlib import Path
 
 import torch
 
 F64 = torch.float64
+
+
+def bf16(value):
+    """To bfloat16 and back: what the serving precision loses where it keeps 16 bits."""
+    return value.to(torch.bfloat16).to(value.dtype)
+
+
+def load_model_dir(path):
+    """(config dict, name -> tensor in float64, integer tensors as they are) of a model folder: the file
+    is a little-endian header length, a JSON header (dtype, shape, byte range per name) and the data."""
+    path = Path(path)
+    config = json.loads((path / "config.json").read_text())
+    blob = (path / "model.safetensors").read_bytes()
+    (header_len,) = struct.unpack("<Q", blob[:8])
+    header = json.loads(blob[8:8 + header_len].decode("utf-8"))
+    data = memoryview(blob)[8 + header_len:]
+    dtypes = {"F64": torch.float64, "F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16,
+              "I32": torch.int32, "I64": torch.int64}
+    weights = {}
+    for name, entry in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = entry["data_offsets"]
+        t = torch.frombuffer(bytearray(data[lo:hi]), dtype=dtypes[entry["dtype"]]).reshape(entry["shape"])
+        weights[name] = t.to(F64) if t.is_floating_point() else t
+    return config, weights
 
 
 def unit(y, eps):
@@ -227,3 +256,12 @@ def forward(config, weights, tokens, rnd=lambda t: t, layers_out=None):
             layers_out.append(x.clone())
     x = unit(x, eps) * w["final.norm"]
     return (rnd(x) @ w["head"].T) * float(config.get("logit_scale", 1.0))
+
+
+def greedy_generate(config, weights, prompt, n_new):
+    """``n_new`` tokens, each the place of the largest logit behind everything so far; the whole sequence
+    is run again for every token."""
+    tokens = [int(t) for t in prompt]
+    for _ in range(n_new):
+        tokens.append(int(forward(config, weights, tokens)[-1].argmax()))
+    return tokens[len(prompt):]

@@ -520,11 +520,11 @@ def test_the_edge_of_a_window(dtype):
 
 def test_kernels_refuse_what_they_cannot_take():
     from flyweight_b200.kernels import KernelError, ops
-    q = torch.zeros(1, 17 * 16, device=DEV)
-    pool = torch.zeros(2, 1, 64, 16, device=DEV)
+    q = torch.zeros(1, 2 * 272, device=DEV)
+    pool = torch.zeros(2, 1, 64, 272, device=DEV)
     i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    with pytest.raises(KernelError, match="unsupported"):     # 17 query heads on one KV head
-        ops.attention_simt(q, pool, pool, i32(0), i32(0), i32(0).reshape(1, 1), 17, 0, 1.0, torch.float32)
+    with pytest.raises(KernelError, match="unsupported"):     # heads of 272 channels
+        ops.attention_simt(q, pool, pool, i32(0), i32(0), i32(0).reshape(1, 1), 2, 0, 1.0, torch.float32)
     with pytest.raises(KernelError, match="unsupported"):     # 17 taps
         ops.shortconv(torch.zeros(1, 12, device=DEV), torch.zeros(4, 17, device=DEV), None,
                       torch.zeros(1, 4, 16, device=DEV), i32(0, 1), i32(0), i32(0), 1, torch.float32)

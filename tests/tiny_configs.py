@@ -196,5 +196,102 @@ DIFORAX_E = {
 TINY.update({"DA": DIFORAX_A, "DB": DIFORAX_B, "DC": DIFORAX_C, "DD": DIFORAX_D, "DE": DIFORAX_E})
 
 
+def _window_attention(heads, kv_heads, dim, vdim, scale, window=None, v_mix=False):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if window is not None:
+        mixer["mask"] = {"size": window}
+    if v_mix:
+        mixer["v_mix"] = True
+    return {"type": "attention", "mixer": mixer}
+
+
+def _pair(left, right):
+    return {"type": "parallel", "mixer": {"left": left, "right": right}}
+
+
+def _left(heads, kv_heads, dim, vdim, scale, rot=None, softcap=None):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot is not None:
+        left["rot"] = rot
+    if softcap is not None:
+        left["softcap"] = softcap
+    return left
+
+
+def _linear(heads, dim, vdim, decay):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay)}
+
+
+# Tiny Gukosun configurations that differ in every size and option: the order of the layers (a pair
+# first, a window first), 1 to 4 query heads per key head, query and value sizes that differ both ways and
+# sizes that are no multiple of 16, partial, full and no rotation with and without the scaling of long
+# waves (the three bands all occur at these sizes), capped and uncapped scores, windows shorter than, equal
+# to and longer than a page and a window of one, layers that mix values beside layers that do not, layers
+# without a feed-forward, models with and without the token side input and the logit scale, decays from
+# fast to almost none, and recurrent states that fill no warp.
+GUKOSUN_A = {
+    "architecture": "Gukosun", "vocab": 211, "width": 80, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+    "token_side": {"dim": 8},
+    "layers": [
+        {**_pair(_left(4, 2, 16, 24, 0.3, rot={"base": 10000.0, "dims": 8, "scaling":
+                                               {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}}, softcap=5.0),
+                 _linear(3, 8, 20, (0.5, 0.9, 0.995))), "mlp": _dense(144)},
+        {**_window_attention(6, 3, 32, 16, 0.2, window=37, v_mix=True), "mlp": _dense(112)},
+        {**_window_attention(2, 1, 24, 24, 0.25), "mlp": None},
+        {**_window_attention(6, 3, 32, 16, 0.3, window=70, v_mix=True), "mlp": _dense(96)},
+        {**_pair(_left(2, 2, 32, 16, 0.2, rot={"base": 500.0, "dims": 32}, softcap=2.0),
+                 _linear(1, 40, 12, (0.97,))), "mlp": None},
+        {**_window_attention(6, 3, 32, 16, 0.3, window=1, v_mix=True), "mlp": _dense(96)},
+    ],
+}
+
+GUKOSUN_B = {
+    "architecture": "Gukosun", "vocab": 130, "width": 96, "norm": {"eps": 1e-6},
+    "layers": [
+        {**_window_attention(4, 4, 16, 48, 0.25, window=64, v_mix=True), "mlp": _dense(160)},
+        {**_pair(_left(3, 1, 20, 20, 0.22), _linear(2, 24, 24, (0.8, 0.999))), "mlp": _dense(120)},
+        {**_window_attention(4, 4, 16, 48, 0.3, window=5, v_mix=True), "mlp": None},
+        {**_window_attention(1, 1, 64, 32, 0.11, window=200), "mlp": _dense(64)},
+    ],
+}
+
+# Head sizes and group widths that the tensor-core attention kernels take, so that the bfloat16 path
+# runs them with a sink, a window and capped scores: 64 and 128 channels, four query heads per key head.
+GUKOSUN_C = {
+    "architecture": "Gukosun", "vocab": 300, "width": 128, "norm": {"eps": 1e-5}, "logit_scale": 2.0,
+    "token_side": {"dim": 16},
+    "layers": [
+        {**_window_attention(8, 2, 64, 64, 0.12, window=130, v_mix=True), "mlp": _dense(256)},
+        {**_pair(_left(8, 2, 128, 128, 0.09, rot={"base": 10000.0, "dims": 64, "scaling":
+                                                  {"factor": 8.0, "low": 1.0, "high": 2.0, "original": 128}}, softcap=10.0),
+                 _linear(2, 64, 64, (0.9, 0.99))), "mlp": _dense(192)},
+        {**_window_attention(8, 2, 64, 64, 0.1, window=70, v_mix=True), "mlp": _dense(256)},
+        {**_pair(_left(4, 1, 64, 64, 0.12, rot={"base": 1000000.0, "dims": 64}),
+                 _linear(4, 32, 32, (0.6, 0.9, 0.97, 0.999))), "mlp": _dense(128)},
+    ],
+}
+
+# Models of one kind of layer only: pairs alone (pages of every key and a state, no window group), and
+# windows alone (no state slots are needed; the first layer does not mix values, the second is the source).
+GUKOSUN_D = {
+    "architecture": "Gukosun", "vocab": 97, "width": 48, "norm": {"eps": 1e-6}, "token_side": {"dim": 4},
+    "layers": [
+        {**_pair(_left(2, 1, 16, 16, 0.25, rot={"base": 100.0, "dims": 16}, softcap=50.0),
+                 _linear(3, 12, 20, (0.7, 0.9, 0.99))), "mlp": _dense(80)},
+        {**_pair(_left(3, 3, 8, 8, 0.35, rot={"base": 10000.0, "dims": 4}), _linear(2, 16, 8, (0.95, 0.5))), "mlp": None},
+    ],
+}
+GUKOSUN_E = {
+    "architecture": "Gukosun", "vocab": 160, "width": 64, "norm": {"eps": 1e-5}, "logit_scale": 0.25,
+    "layers": [
+        {**_window_attention(4, 2, 16, 32, 0.3, window=33), "mlp": _dense(96)},
+        {**_window_attention(2, 2, 32, 16, 0.2, window=64, v_mix=True), "mlp": _dense(64)},
+        {**_window_attention(2, 2, 32, 16, 0.2, v_mix=True), "mlp": _dense(64)},
+    ],
+}
+
+TINY.update({"GA": GUKOSUN_A, "GB": GUKOSUN_B, "GC": GUKOSUN_C, "GD": GUKOSUN_D, "GE": GUKOSUN_E})
+
+
 def vocab_of(config: dict) -> int:
     return int(config.get("vocab_size", config.get("vocab")))
