@@ -105,6 +105,281 @@ decay_scan_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// The same recurrence over portions of prompts, 64 tokens at a time on tensor cores (the serving path in
+// bfloat16).  With S the state in front of a run of n tokens and g the head's decay, token i of the run
+// (counted from 0) reads
+//
+//   o_i = g^(i+1) S^T q_i + sum_{j <= i} g^(i-j) (q_i . k_j) v_j
+//
+// and the run leaves  S' = g^n S + sum_j g^(n-1-j) k_j v_j^T.  One block owns 32 columns of one head's
+// state for one segment and walks its runs in order; a warp owns 16 tokens of the run.  q, k and v enter
+// the products as bfloat16 (silu of the fp32 projection, rounded once); everything else -- the state, the
+// powers of the decay, the decayed scores -- is fp32, and wherever an fp32 quantity is an operand of a
+// tensor-core product (the state in q.S, the decayed scores in P.V, the decayed keys in k v^T) it enters as
+// the sum of two bfloat16 numbers (the value rounded, and what the rounding left), two products into one
+// fp32 accumulator, so that no more than about 2^-17 of it is lost.
+//
+// A long segment is cut into pieces of `piece_len` tokens (a multiple of RUN) that run side by side: a first
+// launch sums what each piece alone adds to the state (from zero), a small kernel chains those sums into
+// the state in front of every piece, and the main launch then walks every piece from its own start.  Only
+// a segment's last piece writes the slot.  Segments of one piece skip the first two launches' work.
+constexpr int RUN = 64;        // tokens per run
+constexpr int CT = 32;         // state columns per block
+constexpr int PAD = 8;         // bf16 entries behind every shared row (rows then start 4 banks apart)
+constexpr int SF = CT + 4;     // fp32 entries per row of the state's master copy
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t ld32(const __nv_bfloat16* at) { return *reinterpret_cast<const uint32_t*>(at); }
+// x = hi + lo with hi = bf16(x): the two halves of an fp32 operand
+__device__ __forceinline__ void split_bf16(float x, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(x);
+    lo = __float2bfloat16_rn(x - __bfloat162float(hi));
+}
+__device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint32_t& lo) {
+    __nv_bfloat16 xh, xl, yh, yl;
+    split_bf16(x, xh, xl);
+    split_bf16(y, yh, yl);
+    __nv_bfloat162 h2(xh, yh), l2(xl, yl);
+    hi = *reinterpret_cast<uint32_t*>(&h2);
+    lo = *reinterpret_cast<uint32_t*>(&l2);
+}
+__device__ __forceinline__ float silu_quick(float x) { return x * __frcp_rn(1.0f + __expf(-x)); }
+
+// SUMS: the first launch (what a piece adds to a zero state, written to `scratch`; no read-out).
+template <bool SUMS>
+__global__ void __launch_bounds__(128)
+decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, int k_col, int v_col, int act_silu,
+                  const float* __restrict__ decay, float* __restrict__ state, long long slot_stride,
+                  const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                  const int* __restrict__ piece_seg, const int* __restrict__ piece_tok0, int piece_len,
+                  float* __restrict__ scratch, float* __restrict__ o, int H, int d, int e, int DP) {
+    fwb::pdl_entry();
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int QS = DP + PAD, TS = RUN + PAD;           // row strides: [token][channel] and [channel][token]
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [RUN][QS]
+    __nv_bfloat16* Ks = Qs + RUN * QS;                                  // [RUN][QS]
+    __nv_bfloat16* KThi = Ks + RUN * QS;                                // [DP][TS]   decayed keys, by channel
+    __nv_bfloat16* KTlo = KThi + DP * TS;
+    __nv_bfloat16* VT = KTlo + DP * TS;                                 // [CT][TS]   values, by column
+    __nv_bfloat16* SThi = VT + CT * TS;                                 // [CT][QS]   the state, by column
+    __nv_bfloat16* STlo = SThi + CT * QS;
+    float* Sf = reinterpret_cast<float*>(STlo + CT * QS);               // [DP][SF]   the state itself
+    float* pw = Sf + DP * SF;                                           // [RUN + 1]  powers of the decay
+
+    const int piece = blockIdx.x, h = blockIdx.y, e0 = blockIdx.z * CT;
+    const int seg = piece_seg[piece], first = piece_tok0[piece], seg_end = seg_start[seg + 1];
+    const int last = first + piece_len < seg_end ? first + piece_len : seg_end;
+    const bool head = first == seg_start[seg], tail = last == seg_end;
+    if (SUMS && tail) return;                          // nothing follows this piece: its sum is not needed
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int dp16 = DP >> 4;
+    const size_t head_at = (size_t)h * d * e;
+    float* mine = state + (size_t)seg_slot[seg] * slot_stride + head_at;
+    float* held = scratch ? scratch + (size_t)piece * H * d * e + head_at : nullptr;
+    // the state in front of the piece: the slot's for a segment of one piece, else what the chain left (also
+    // for a first piece, since the last piece of its segment writes the slot in the same launch)
+    const float* front = SUMS ? nullptr : (head && tail ? mine : held);
+    float* behind = SUMS ? held : (tail ? mine : nullptr);
+
+    for (int i = tid; i <= RUN; i += blockDim.x) pw[i] = (float)pow((double)decay[h], (double)i);
+    for (int i = tid; i < DP * CT; i += blockDim.x) {
+        const int r = i / CT, c = i - r * CT;
+        Sf[r * SF + c] = (front && r < d && e0 + c < e) ? front[(size_t)r * e + e0 + c] : 0.0f;
+    }
+
+    for (int t0 = first; t0 < last; t0 += RUN) {
+        const int n = last - t0 < RUN ? last - t0 : RUN;
+        __syncthreads();                                   // the run before is done with the shared rows
+        for (int i = tid; i < RUN * DP; i += blockDim.x) {
+            const int tok = i / DP, r = i - tok * DP;
+            float qv = 0.0f, kv = 0.0f;
+            if (tok < n && r < d) {
+                const float* src = p + (size_t)(t0 + tok) * row_stride + (size_t)h * d + r;
+                if (!SUMS) qv = src[q_col];
+                kv = src[k_col];
+                if (act_silu) {
+                    qv = silu_quick(qv);
+                    kv = silu_quick(kv);
+                }
+            }
+            const __nv_bfloat16 kb = __float2bfloat16_rn(kv);
+            if (!SUMS) {
+                Qs[tok * QS + r] = __float2bfloat16_rn(qv);
+                Ks[tok * QS + r] = kb;
+            }
+            // the key as the state takes it: the rounded key times g^(n-1-tok), in two halves
+            __nv_bfloat16 hi, lo;
+            split_bf16(tok < n ? __bfloat162float(kb) * pw[n - 1 - tok] : 0.0f, hi, lo);
+            KThi[r * TS + tok] = hi;
+            KTlo[r * TS + tok] = lo;
+        }
+        for (int i = tid; i < RUN * CT; i += blockDim.x) {
+            const int tok = i / CT, c = i - tok * CT;
+            float v = 0.0f;
+            if (tok < n && e0 + c < e) {
+                v = p[(size_t)(t0 + tok) * row_stride + v_col + (size_t)h * e + e0 + c];
+                if (act_silu) v = silu_quick(v);
+            }
+            VT[c * TS + tok] = __float2bfloat16_rn(v);
+        }
+        for (int i = tid; !SUMS && i < DP * CT; i += blockDim.x) {
+            const int r = i / CT, c = i - r * CT;
+            __nv_bfloat16 hi, lo;
+            split_bf16(Sf[r * SF + c], hi, lo);
+            SThi[c * QS + r] = hi;
+            STlo[c * QS + r] = lo;
+        }
+        __syncthreads();
+
+        const int row0 = warp * 16;                        // this warp's tokens of the run: row0 .. row0 + 15
+        if (!SUMS && row0 < n) {
+            const __nv_bfloat16* qa = Qs + (row0 + g) * QS + 2 * t;
+            float acc[CT / 8][4];
+#pragma unroll
+            for (int nt = 0; nt < CT / 8; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[nt][j] = 0.0f;
+            // what the state in front of the run gives: (q . S) g^(i+1)
+            for (int ks = 0; ks < dp16; ++ks) {
+                uint32_t a[4] = {ld32(qa + ks * 16), ld32(qa + 8 * QS + ks * 16), ld32(qa + ks * 16 + 8),
+                                 ld32(qa + 8 * QS + ks * 16 + 8)};
+#pragma unroll
+                for (int nt = 0; nt < CT / 8; ++nt) {
+                    const int at = (nt * 8 + g) * QS + ks * 16 + 2 * t;
+                    mma_bf16(acc[nt], a, ld32(SThi + at), ld32(SThi + at + 8));
+                    mma_bf16(acc[nt], a, ld32(STlo + at), ld32(STlo + at + 8));
+                }
+            }
+            const float up = pw[row0 + g + 1], down = pw[row0 + g + 9];
+#pragma unroll
+            for (int nt = 0; nt < CT / 8; ++nt) {
+                acc[nt][0] *= up;
+                acc[nt][1] *= up;
+                acc[nt][2] *= down;
+                acc[nt][3] *= down;
+            }
+            // the run's own keys, 16 at a time up to this warp's last token: decayed scores, then P.V
+            for (int kk = 0; kk <= warp; ++kk) {
+                float sc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+                for (int ks = 0; ks < dp16; ++ks) {
+                    uint32_t a[4] = {ld32(qa + ks * 16), ld32(qa + 8 * QS + ks * 16), ld32(qa + ks * 16 + 8),
+                                     ld32(qa + 8 * QS + ks * 16 + 8)};
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int at = (kk * 16 + half * 8 + g) * QS + ks * 16 + 2 * t;
+                        mma_bf16(sc[half], a, ld32(Ks + at), ld32(Ks + at + 8));
+                    }
+                }
+                uint32_t ahi[4], alo[4];
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+#pragma unroll
+                    for (int rr = 0; rr < 2; ++rr) {
+                        const int i = row0 + g + 8 * rr, j = kk * 16 + half * 8 + 2 * t;
+                        const float w0 = j <= i ? sc[half][2 * rr] * pw[i - j] : 0.0f;
+                        const float w1 = j + 1 <= i ? sc[half][2 * rr + 1] * pw[i - j - 1] : 0.0f;
+                        split_pair(w0, w1, ahi[2 * half + rr], alo[2 * half + rr]);
+                    }
+#pragma unroll
+                for (int nt = 0; nt < CT / 8; ++nt) {
+                    const int at = (nt * 8 + g) * TS + kk * 16 + 2 * t;
+                    const uint32_t b0 = ld32(VT + at), b1 = ld32(VT + at + 8);
+                    mma_bf16(acc[nt], ahi, b0, b1);
+                    mma_bf16(acc[nt], alo, b0, b1);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < CT / 8; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = row0 + g + 8 * (j >> 1), c = e0 + nt * 8 + 2 * t + (j & 1);
+                    if (i < n && c < e) o[(size_t)(t0 + i) * H * e + (size_t)h * e + c] = acc[nt][j];
+                }
+        }
+        // the state behind the run: 16 of its rows at a time, a warp each
+        const float shrink = pw[n];
+        const int steps = (n + 15) >> 4;
+        for (int mt = warp; mt < dp16; mt += 4) {
+            float* srow = Sf + (mt * 16 + g) * SF + 2 * t;
+            float acc[CT / 8][4];
+#pragma unroll
+            for (int nt = 0; nt < CT / 8; ++nt) {
+                acc[nt][0] = srow[nt * 8] * shrink;
+                acc[nt][1] = srow[nt * 8 + 1] * shrink;
+                acc[nt][2] = srow[8 * SF + nt * 8] * shrink;
+                acc[nt][3] = srow[8 * SF + nt * 8 + 1] * shrink;
+            }
+            for (int ks = 0; ks < steps; ++ks) {
+                const int at = (mt * 16 + g) * TS + ks * 16 + 2 * t;
+                uint32_t ahi[4] = {ld32(KThi + at), ld32(KThi + at + 8 * TS), ld32(KThi + at + 8), ld32(KThi + at + 8 * TS + 8)};
+                uint32_t alo[4] = {ld32(KTlo + at), ld32(KTlo + at + 8 * TS), ld32(KTlo + at + 8), ld32(KTlo + at + 8 * TS + 8)};
+#pragma unroll
+                for (int nt = 0; nt < CT / 8; ++nt) {
+                    const int bt = (nt * 8 + g) * TS + ks * 16 + 2 * t;
+                    const uint32_t b0 = ld32(VT + bt), b1 = ld32(VT + bt + 8);
+                    mma_bf16(acc[nt], ahi, b0, b1);
+                    mma_bf16(acc[nt], alo, b0, b1);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < CT / 8; ++nt) {
+                srow[nt * 8] = acc[nt][0];
+                srow[nt * 8 + 1] = acc[nt][1];
+                srow[8 * SF + nt * 8] = acc[nt][2];
+                srow[8 * SF + nt * 8 + 1] = acc[nt][3];
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; behind && i < DP * CT; i += blockDim.x) {
+        const int r = i / CT, c = i - r * CT;
+        if (r < d && e0 + c < e) behind[(size_t)r * e + e0 + c] = Sf[r * SF + c];
+    }
+}
+
+// Chains the pieces' sums: walking a segment's pieces in order, every piece's entry of `scratch` (what the
+// piece alone adds) is replaced by the state in front of that piece.  One thread per state entry; blocks of
+// pieces that are not the first of a segment of several pieces have nothing to do.
+__global__ void __launch_bounds__(256)
+decay_chain_kernel(const float* __restrict__ decay, const float* __restrict__ state, long long slot_stride,
+                   const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                   const int* __restrict__ piece_seg, const int* __restrict__ piece_tok0, int piece_len,
+                   float* __restrict__ scratch, int H, int d, int e) {
+    fwb::pdl_entry();
+    const int piece = blockIdx.x;
+    const int seg = piece_seg[piece], first = piece_tok0[piece], seg_end = seg_start[seg + 1];
+    if (first != seg_start[seg] || first + piece_len >= seg_end) return;
+    const size_t size = (size_t)H * d * e;
+    const size_t at = (size_t)blockIdx.y * blockDim.x + threadIdx.x;
+    if (at >= size) return;
+    const int h = (int)(at / ((size_t)d * e));
+    const float shrink = (float)pow((double)decay[h], (double)piece_len);
+    float run = state[(size_t)seg_slot[seg] * slot_stride + at];
+    for (int c = piece;; ++c) {
+        float* cell = scratch + (size_t)c * size + at;
+        if (piece_tok0[c] + piece_len >= seg_end) {        // the segment's last piece
+            *cell = run;
+            break;
+        }
+        const float sum = *cell;
+        *cell = run;
+        run = shrink * run + sum;
+    }
+}
+
+size_t decay_runs_smem(int DP) {
+    const size_t QS = DP + PAD, TS = RUN + PAD;
+    return (2 * RUN * QS + 2 * (size_t)DP * TS + CT * TS + 2 * CT * QS) * sizeof(__nv_bfloat16)
+           + ((size_t)DP * SF + RUN + 1) * sizeof(float);
+}
+
 }  // namespace
 
 // p: fp32 rows of `row_stride` entries, one per token, that hold q [H][d] from column q_col, k [H][d] from
@@ -129,5 +404,49 @@ FWB_API int fwb_decay_scan(const float* p, long long row_stride, int q_col, int 
     }
     fwb::pdl(decay_scan_kernel, dim3(S, H, tiles), COLS * splits, smem, stream)(
         p, row_stride, q_col, k_col, v_col, act_silu, decay, state, slot_stride, seg_start, seg_slot, o, H, d, e);
+    return fwb_launch_status();
+}
+
+// The same operation, 64 tokens of a segment at a time on tensor cores: q, k and v enter as bfloat16, the
+// state, the decay's powers and every sum stay fp32.  For steps that bring portions of prompts; heads of up
+// to 256 channels (FWB_UNSUPPORTED beyond: the token-by-token form takes those).  The segments come cut into
+// `P` pieces of at most `piece_len` tokens (a multiple of 64): piece_seg, piece_tok0.  `scratch`: fp32
+// [P][H d e], needed when some segment has more than one piece (`chained` != 0), else it may be null.
+FWB_API int fwb_decay_runs(const float* p, long long row_stride, int q_col, int k_col, int v_col, int act_silu,
+                           const float* decay, float* state, long long slot_stride, const int* seg_start,
+                           const int* seg_slot, const int* piece_seg, const int* piece_tok0, int piece_len,
+                           int chained, float* scratch, float* o, int T, int S, int P, int H, int d, int e,
+                           cudaStream_t stream) {
+    if (T <= 0 || S <= 0 || P <= 0) return FWB_OK;
+    if (!p || !decay || !state || !seg_start || !seg_slot || !piece_seg || !piece_tok0 || !o) return FWB_BAD_ARGUMENT;
+    if (H <= 0 || d <= 0 || e <= 0 || q_col < 0 || k_col < 0 || v_col < 0) return FWB_BAD_ARGUMENT;
+    if (piece_len <= 0 || piece_len % RUN != 0 || (chained && !scratch)) return FWB_BAD_ARGUMENT;
+    if (row_stride < (long long)H * d || slot_stride < (long long)H * d * e) return FWB_BAD_ARGUMENT;
+    if (d > 256) return FWB_UNSUPPORTED;
+    const int tiles = (e + CT - 1) / CT;
+    const size_t size = (size_t)H * d * e;
+    if (H > 65535 || tiles > 65535 || (size + 255) / 256 > 65535) return FWB_TOO_LARGE;
+    const int DP = (d + 15) / 16 * 16;
+    const size_t smem = decay_runs_smem(DP);
+    if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(decay_runs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err == cudaSuccess)
+            err = cudaFuncSetAttribute(decay_runs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+    }
+    if (chained) {
+        fwb::pdl(decay_runs_kernel<true>, dim3(P, H, tiles), 128, smem, stream)(
+            p, row_stride, q_col, k_col, v_col, act_silu, decay, state, slot_stride, seg_start, seg_slot, piece_seg,
+            piece_tok0, piece_len, scratch, o, H, d, e, DP);
+        int status = fwb_launch_status();
+        if (status != FWB_OK) return status;
+        fwb::pdl(decay_chain_kernel, dim3(P, (unsigned)((size + 255) / 256)), 256, 0, stream)(
+            decay, state, slot_stride, seg_start, seg_slot, piece_seg, piece_tok0, piece_len, scratch, H, d, e);
+        status = fwb_launch_status();
+        if (status != FWB_OK) return status;
+    }
+    fwb::pdl(decay_runs_kernel<false>, dim3(P, H, tiles), 128, smem, stream)(
+        p, row_stride, q_col, k_col, v_col, act_silu, decay, state, slot_stride, seg_start, seg_slot, piece_seg,
+        piece_tok0, piece_len, chained ? scratch : nullptr, o, H, d, e, DP);
     return fwb_launch_status();
 }

@@ -167,3 +167,37 @@ def decay_scan(p: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch
              ptr(decay), ptr(state), c_longlong(stride), ptr(batch.seg_start), ptr(batch.seg_slot), ptr(o), T, S,
              heads, dim, vdim, stream())
     return o
+
+
+PIECE_TOKENS = 256      # tokens of a segment that one block of the tensor-core recurrence walks
+
+
+def decay_runs(p: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
+               batch, heads: int, dim: int, vdim: int, act_silu: bool = True) -> torch.Tensor:
+    """``decay_scan`` for steps that bring portions of prompts, on tensor cores: q, k and v enter the
+    products as bfloat16, the state and every sum stay fp32.  Segments longer than ``PIECE_TOKENS`` are cut
+    into pieces that run side by side (their contributions to the state are chained first)."""
+    check_tensor("projection", p, torch.float32)
+    T, width = p.shape
+    if max(q_col, k_col) + heads * dim > width or v_col + heads * vdim > width:
+        raise KernelError("the projection's rows are shorter than the columns asked for")
+    check_tensor("decay", decay, torch.float32, (heads,))
+    size = heads * dim * vdim
+    if (not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] < size
+            or state.stride(1) != 1):
+        raise KernelError(f"the recurrent state must be CUDA fp32 [slots][>= {size}], got {tuple(state.shape)}")
+    stride = state.stride(0) if state.shape[0] > 1 else state.shape[1]
+    S = batch.n_segments
+    _i32("seg_start", batch.seg_start, S + 1)
+    _i32("seg_slot", batch.seg_slot, S)
+    piece_seg, piece_tok0, pieces = batch.attention_tiles(PIECE_TOKENS, 0)
+    chained = batch.max_segment > PIECE_TOKENS
+    scratch = torch.empty((pieces, size), dtype=torch.float32, device=p.device) if chained else None
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=p.device)
+    lib.call("fwb_decay_runs", ptr(p), c_longlong(width), int(q_col), int(k_col), int(v_col), 1 if act_silu else 0,
+             ptr(decay), ptr(state), c_longlong(stride), ptr(batch.seg_start), ptr(batch.seg_slot),
+             ptr(piece_seg), ptr(piece_tok0), PIECE_TOKENS, 1 if chained else 0,
+             ptr(scratch) if chained else None, ptr(o), T, S, pieces, heads, dim, vdim, stream())
+    if chained:
+        lib.add_launches(2)
+    return o

@@ -25,6 +25,7 @@ class DecayedLinearAttention(Mixer):
     """params: hidden_size, num_heads, dim, vdim, decay (one number per head), eps (of the output's norm).
     tensors: q, k [heads dim][H]; v, g [heads vdim][H]; norm [heads vdim]; o [H][heads vdim]."""
     graph_safe = True
+    RUNS_FROM = 16      # the longest portion of a step from which the tensor-core form takes the step
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -79,8 +80,13 @@ class DecayedLinearAttention(Mixer):
 
     def forward(self, ctx, h, cache):
         p = ops.linear(h, self.w_in, torch.float32)
-        o = mixing.decay_scan(p, 0, self._qk, 2 * self._qk, self.decay, cache.state, ctx.batch, self.n_heads,
-                              self.dim, self.vdim, act_silu=True)
+        # portions of prompts in bfloat16 walk 64 tokens at a time on tensor cores (q, k, v rounded to bfloat16,
+        # the state and the sums in fp32); single tokens, short portions and 32-bit runs go token by token
+        runs = (ctx.precision.act_dtype == torch.bfloat16 and self.dim <= 256
+                and getattr(ctx.batch, "max_segment", 1) >= self.RUNS_FROM)
+        o = (mixing.decay_runs if runs else mixing.decay_scan)(
+            p, 0, self._qk, 2 * self._qk, self.decay, cache.state, ctx.batch, self.n_heads, self.dim, self.vdim,
+            act_silu=True)
         gate_at = 2 * self._qk + self._v
         z = mixing.gated_rmsnorm(o, p[:, gate_at:gate_at + self._v], self.norm, self.eps, ctx.precision.act_dtype)
         return ops.linear(z, self.w_o, torch.float32)
