@@ -117,7 +117,7 @@ decay_scan_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
 // state for one segment and walks its runs in order; a warp owns 16 tokens of the run.  q, k and v enter
 // the products as bfloat16 (silu of the fp32 projection, rounded once); everything else -- the state, the
 // powers of the decay, the decayed scores -- is fp32, and wherever an fp32 quantity is an operand of a
-// tensor-core product (the state in q.S, the decayed scores in P.V, the decayed keys in k v^T) it enters as
+// tensor-core product (the state in q.S, the decayed scores in P.V, the decayed values in k v^T) it enters as
 // the sum of two bfloat16 numbers (the value rounded, and what the rounding left), two products into one
 // fp32 accumulator, so that no more than about 2^-17 of it is lost.
 //
@@ -152,9 +152,38 @@ __device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint3
 }
 __device__ __forceinline__ float silu_quick(float x) { return x * __frcp_rn(1.0f + __expf(-x)); }
 
+// four 8x8 tiles of bfloat16, each transposed on the way: lane l gives the address of row l % 8 of tile l / 8
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], const __nv_bfloat16* row) {
+    const uint32_t at = (uint32_t)__cvta_generic_to_shared(row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(at));
+}
+// four consecutive floats of which `left` exist (VEC: one 16-byte load; the caller has checked the alignment)
+template <bool VEC>
+__device__ __forceinline__ float4 take4(const float* at, int left) {
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (left <= 0) return v;
+    if (VEC) return *reinterpret_cast<const float4*>(at);
+    v.x = at[0];
+    if (left > 1) v.y = at[1];
+    if (left > 2) v.z = at[2];
+    if (left > 3) v.w = at[3];
+    return v;
+}
+__device__ __forceinline__ float4 silu4(float4 v) {
+    return make_float4(silu_quick(v.x), silu_quick(v.y), silu_quick(v.z), silu_quick(v.w));
+}
+__device__ __forceinline__ uint2 pack4(float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    return make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
 // SUMS: the first launch (what a piece adds to a zero state, written to `scratch`; no read-out).
-template <bool SUMS>
-__global__ void __launch_bounds__(128)
+// Shared rows are [token][channel] throughout; the products that want them the other way round (keys as
+// rows of k v^T, values as columns of P.V) take them through transposing ldmatrix loads.  The decay of the
+// state's update rides on the values: S' = g^n S + sum_j k_j (g^(n-1-j) v_j)^T, so the keys enter exactly.
+template <bool SUMS, bool VEC>
+__global__ void __launch_bounds__(128, 2)
 decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, int k_col, int v_col, int act_silu,
                   const float* __restrict__ decay, float* __restrict__ state, long long slot_stride,
                   const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
@@ -162,13 +191,14 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
                   float* __restrict__ scratch, float* __restrict__ o, int H, int d, int e, int DP) {
     fwb::pdl_entry();
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    const int QS = DP + PAD, TS = RUN + PAD;           // row strides: [token][channel] and [channel][token]
+    const int QS = DP + PAD;                           // entries per row of the [token][channel] arrays
+    constexpr int VS = CT + PAD;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [RUN][QS]
     __nv_bfloat16* Ks = Qs + RUN * QS;                                  // [RUN][QS]
-    __nv_bfloat16* KThi = Ks + RUN * QS;                                // [DP][TS]   decayed keys, by channel
-    __nv_bfloat16* KTlo = KThi + DP * TS;
-    __nv_bfloat16* VT = KTlo + DP * TS;                                 // [CT][TS]   values, by column
-    __nv_bfloat16* SThi = VT + CT * TS;                                 // [CT][QS]   the state, by column
+    __nv_bfloat16* Vs = Ks + RUN * QS;                                  // [RUN][VS]  values
+    __nv_bfloat16* Vdhi = Vs + RUN * VS;                                // [RUN][VS]  values times g^(n-1-token)
+    __nv_bfloat16* Vdlo = Vdhi + RUN * VS;
+    __nv_bfloat16* SThi = Vdlo + RUN * VS;                              // [CT][QS]   the state, by column
     __nv_bfloat16* STlo = SThi + CT * QS;
     float* Sf = reinterpret_cast<float*>(STlo + CT * QS);               // [DP][SF]   the state itself
     float* pw = Sf + DP * SF;                                           // [RUN + 1]  powers of the decay
@@ -179,7 +209,7 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
     const bool head = first == seg_start[seg], tail = last == seg_end;
     if (SUMS && tail) return;                          // nothing follows this piece: its sum is not needed
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int dp16 = DP >> 4;
+    const int dp16 = DP >> 4, d4 = DP >> 2;
     const size_t head_at = (size_t)h * d * e;
     float* mine = state + (size_t)seg_slot[seg] * slot_stride + head_at;
     float* held = scratch ? scratch + (size_t)piece * H * d * e + head_at : nullptr;
@@ -197,37 +227,47 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
     for (int t0 = first; t0 < last; t0 += RUN) {
         const int n = last - t0 < RUN ? last - t0 : RUN;
         __syncthreads();                                   // the run before is done with the shared rows
-        for (int i = tid; i < RUN * DP; i += blockDim.x) {
-            const int tok = i / DP, r = i - tok * DP;
-            float qv = 0.0f, kv = 0.0f;
-            if (tok < n && r < d) {
+        // q and k: four channels a thread and four such groups in flight
+        for (int base = tid; base < RUN * d4; base += 4 * 128) {
+            float4 qv[4], kv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + u * 128, tok = i / d4, r = (i - tok * d4) << 2;
+                const int left = (i < RUN * d4 && tok < n) ? d - r : 0;
                 const float* src = p + (size_t)(t0 + tok) * row_stride + (size_t)h * d + r;
-                if (!SUMS) qv = src[q_col];
-                kv = src[k_col];
-                if (act_silu) {
-                    qv = silu_quick(qv);
-                    kv = silu_quick(kv);
-                }
+                qv[u] = SUMS ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : take4<VEC>(src + q_col, left);
+                kv[u] = take4<VEC>(src + k_col, left);
             }
-            const __nv_bfloat16 kb = __float2bfloat16_rn(kv);
-            if (!SUMS) {
-                Qs[tok * QS + r] = __float2bfloat16_rn(qv);
-                Ks[tok * QS + r] = kb;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = base + u * 128, tok = i / d4, r = (i - tok * d4) << 2;
+                if (i >= RUN * d4) break;
+                if (!SUMS) *reinterpret_cast<uint2*>(Qs + tok * QS + r) = pack4(act_silu ? silu4(qv[u]) : qv[u]);
+                *reinterpret_cast<uint2*>(Ks + tok * QS + r) = pack4(act_silu ? silu4(kv[u]) : kv[u]);
             }
-            // the key as the state takes it: the rounded key times g^(n-1-tok), in two halves
-            __nv_bfloat16 hi, lo;
-            split_bf16(tok < n ? __bfloat162float(kb) * pw[n - 1 - tok] : 0.0f, hi, lo);
-            KThi[r * TS + tok] = hi;
-            KTlo[r * TS + tok] = lo;
         }
-        for (int i = tid; i < RUN * CT; i += blockDim.x) {
-            const int tok = i / CT, c = i - tok * CT;
-            float v = 0.0f;
-            if (tok < n && e0 + c < e) {
-                v = p[(size_t)(t0 + tok) * row_stride + v_col + (size_t)h * e + e0 + c];
-                if (act_silu) v = silu_quick(v);
+        {   // v: the rounded value, and the rounded value times g^(n-1-token) in two halves
+            float4 vv[RUN * CT / 4 / 128];
+#pragma unroll
+            for (int u = 0; u < RUN * CT / 4 / 128; ++u) {
+                const int i = tid + u * 128, tok = i / (CT / 4), c = (i % (CT / 4)) << 2;
+                vv[u] = take4<VEC>(p + (size_t)(t0 + tok) * row_stride + v_col + (size_t)h * e + e0 + c,
+                                   tok < n ? e - (e0 + c) : 0);
             }
-            VT[c * TS + tok] = __float2bfloat16_rn(v);
+#pragma unroll
+            for (int u = 0; u < RUN * CT / 4 / 128; ++u) {
+                const int i = tid + u * 128, tok = i / (CT / 4), c = (i % (CT / 4)) << 2;
+                const uint2 packed = pack4(act_silu ? silu4(vv[u]) : vv[u]);
+                if (!SUMS) *reinterpret_cast<uint2*>(Vs + tok * VS + c) = packed;
+                const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&packed.x);
+                const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&packed.y);
+                const float w = tok < n ? pw[n - 1 - tok] : 0.0f;
+                uint2 dh, dl;
+                split_pair(__low2float(lo2) * w, __high2float(lo2) * w, dh.x, dl.x);
+                split_pair(__low2float(hi2) * w, __high2float(hi2) * w, dh.y, dl.y);
+                *reinterpret_cast<uint2*>(Vdhi + tok * VS + c) = dh;
+                *reinterpret_cast<uint2*>(Vdlo + tok * VS + c) = dl;
+            }
         }
         for (int i = tid; !SUMS && i < DP * CT; i += blockDim.x) {
             const int r = i / CT, c = i - r * CT;
@@ -239,6 +279,8 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
         __syncthreads();
 
         const int row0 = warp * 16;                        // this warp's tokens of the run: row0 .. row0 + 15
+        // the address this lane gives to a transposing load of values: 16 tokens by 16 columns
+        const int v_lane = (lane & 15) * VS + ((lane >> 4) << 3);
         if (!SUMS && row0 < n) {
             const __nv_bfloat16* qa = Qs + (row0 + g) * QS + 2 * t;
             float acc[CT / 8][4];
@@ -288,11 +330,13 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
                         split_pair(w0, w1, ahi[2 * half + rr], alo[2 * half + rr]);
                     }
 #pragma unroll
-                for (int nt = 0; nt < CT / 8; ++nt) {
-                    const int at = (nt * 8 + g) * TS + kk * 16 + 2 * t;
-                    const uint32_t b0 = ld32(VT + at), b1 = ld32(VT + at + 8);
-                    mma_bf16(acc[nt], ahi, b0, b1);
-                    mma_bf16(acc[nt], alo, b0, b1);
+                for (int np = 0; np < CT / 16; ++np) {
+                    uint32_t b[4];
+                    ldsm4t(b, Vs + kk * 16 * VS + np * 16 + v_lane);
+                    mma_bf16(acc[2 * np], ahi, b[0], b[1]);
+                    mma_bf16(acc[2 * np], alo, b[0], b[1]);
+                    mma_bf16(acc[2 * np + 1], ahi, b[2], b[3]);
+                    mma_bf16(acc[2 * np + 1], alo, b[2], b[3]);
                 }
             }
 #pragma unroll
@@ -306,6 +350,8 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
         // the state behind the run: 16 of its rows at a time, a warp each
         const float shrink = pw[n];
         const int steps = (n + 15) >> 4;
+        // this lane's address in a transposing load of keys: 16 tokens by 16 channels
+        const int k_lane = ((lane & 7) + ((lane >> 4) << 3)) * QS + (((lane >> 3) & 1) << 3);
         for (int mt = warp; mt < dp16; mt += 4) {
             float* srow = Sf + (mt * 16 + g) * SF + 2 * t;
             float acc[CT / 8][4];
@@ -317,15 +363,17 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
                 acc[nt][3] = srow[8 * SF + nt * 8 + 1] * shrink;
             }
             for (int ks = 0; ks < steps; ++ks) {
-                const int at = (mt * 16 + g) * TS + ks * 16 + 2 * t;
-                uint32_t ahi[4] = {ld32(KThi + at), ld32(KThi + at + 8 * TS), ld32(KThi + at + 8), ld32(KThi + at + 8 * TS + 8)};
-                uint32_t alo[4] = {ld32(KTlo + at), ld32(KTlo + at + 8 * TS), ld32(KTlo + at + 8), ld32(KTlo + at + 8 * TS + 8)};
+                uint32_t a[4];
+                ldsm4t(a, Ks + ks * 16 * QS + mt * 16 + k_lane);
 #pragma unroll
-                for (int nt = 0; nt < CT / 8; ++nt) {
-                    const int bt = (nt * 8 + g) * TS + ks * 16 + 2 * t;
-                    const uint32_t b0 = ld32(VT + bt), b1 = ld32(VT + bt + 8);
-                    mma_bf16(acc[nt], ahi, b0, b1);
-                    mma_bf16(acc[nt], alo, b0, b1);
+                for (int np = 0; np < CT / 16; ++np) {
+                    uint32_t bh[4], bl[4];
+                    ldsm4t(bh, Vdhi + ks * 16 * VS + np * 16 + v_lane);
+                    ldsm4t(bl, Vdlo + ks * 16 * VS + np * 16 + v_lane);
+                    mma_bf16(acc[2 * np], a, bh[0], bh[1]);
+                    mma_bf16(acc[2 * np], a, bl[0], bl[1]);
+                    mma_bf16(acc[2 * np + 1], a, bh[2], bh[3]);
+                    mma_bf16(acc[2 * np + 1], a, bl[2], bl[3]);
                 }
             }
 #pragma unroll
@@ -375,8 +423,8 @@ decay_chain_kernel(const float* __restrict__ decay, const float* __restrict__ st
 }
 
 size_t decay_runs_smem(int DP) {
-    const size_t QS = DP + PAD, TS = RUN + PAD;
-    return (2 * RUN * QS + 2 * (size_t)DP * TS + CT * TS + 2 * CT * QS) * sizeof(__nv_bfloat16)
+    const size_t QS = DP + PAD, VS = CT + PAD;
+    return (2 * RUN * QS + 3 * RUN * VS + 2 * CT * QS) * sizeof(__nv_bfloat16)
            + ((size_t)DP * SF + RUN + 1) * sizeof(float);
 }
 
@@ -428,14 +476,18 @@ FWB_API int fwb_decay_runs(const float* p, long long row_stride, int q_col, int 
     if (H > 65535 || tiles > 65535 || (size + 255) / 256 > 65535) return FWB_TOO_LARGE;
     const int DP = (d + 15) / 16 * 16;
     const size_t smem = decay_runs_smem(DP);
+    // 16-byte loads where every group of four channels starts on such a border
+    const bool vec = d % 4 == 0 && e % 4 == 0 && row_stride % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0
+                     && v_col % 4 == 0 && reinterpret_cast<uintptr_t>(p) % 16 == 0;
+    auto sums = vec ? decay_runs_kernel<true, true> : decay_runs_kernel<true, false>;
+    auto walk = vec ? decay_runs_kernel<false, true> : decay_runs_kernel<false, false>;
     if (smem > 48 * 1024) {
-        cudaError_t err = cudaFuncSetAttribute(decay_runs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err == cudaSuccess)
-            err = cudaFuncSetAttribute(decay_runs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(sums, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(walk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
     }
     if (chained) {
-        fwb::pdl(decay_runs_kernel<true>, dim3(P, H, tiles), 128, smem, stream)(
+        fwb::pdl(sums, dim3(P, H, tiles), 128, smem, stream)(
             p, row_stride, q_col, k_col, v_col, act_silu, decay, state, slot_stride, seg_start, seg_slot, piece_seg,
             piece_tok0, piece_len, scratch, o, H, d, e, DP);
         int status = fwb_launch_status();
@@ -445,7 +497,7 @@ FWB_API int fwb_decay_runs(const float* p, long long row_stride, int q_col, int 
         status = fwb_launch_status();
         if (status != FWB_OK) return status;
     }
-    fwb::pdl(decay_runs_kernel<false>, dim3(P, H, tiles), 128, smem, stream)(
+    fwb::pdl(walk, dim3(P, H, tiles), 128, smem, stream)(
         p, row_stride, q_col, k_col, v_col, act_silu, decay, state, slot_stride, seg_start, seg_slot, piece_seg,
         piece_tok0, piece_len, chained ? scratch : nullptr, o, H, d, e, DP);
     return fwb_launch_status();
