@@ -114,7 +114,7 @@ decay_scan_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
 //   o_i = g^(i+1) S^T q_i + sum_{j <= i} g^(i-j) (q_i . k_j) v_j
 //
 // and the run leaves  S' = g^n S + sum_j g^(n-1-j) k_j v_j^T.  One block owns 32 columns of one head's
-// state for one segment and walks its runs in order; a warp owns 16 tokens of the run.  q, k and v enter
+// state for one piece of a segment and walks its runs in order; a warp owns 16 tokens of the run and 16 columns.  q, k and v enter
 // the products as bfloat16 (silu of the fp32 projection, rounded once); everything else -- the state, the
 // powers of the decay, the decayed scores -- is fp32, and wherever an fp32 quantity is an operand of a
 // tensor-core product (the state in q.S, the decayed scores in P.V, the decayed values in k v^T) it enters as
@@ -129,6 +129,7 @@ constexpr int RUN = 64;        // tokens per run
 constexpr int CT = 32;         // state columns per block
 constexpr int PAD = 8;         // bf16 entries behind every shared row (rows then start 4 banks apart)
 constexpr int SF = CT + 4;     // fp32 entries per row of the state's master copy
+constexpr int THREADS = 256;   // eight warps: four bands of 16 tokens by two halves of the columns
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -183,7 +184,7 @@ __device__ __forceinline__ uint2 pack4(float4 v) {
 // rows of k v^T, values as columns of P.V) take them through transposing ldmatrix loads.  The decay of the
 // state's update rides on the values: S' = g^n S + sum_j k_j (g^(n-1-j) v_j)^T, so the keys enter exactly.
 template <bool SUMS, bool VEC>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(THREADS, 2)
 decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, int k_col, int v_col, int act_silu,
                   const float* __restrict__ decay, float* __restrict__ state, long long slot_stride,
                   const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
@@ -228,11 +229,11 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
         const int n = last - t0 < RUN ? last - t0 : RUN;
         __syncthreads();                                   // the run before is done with the shared rows
         // q and k: four channels a thread and four such groups in flight
-        for (int base = tid; base < RUN * d4; base += 4 * 128) {
+        for (int base = tid; base < RUN * d4; base += 4 * THREADS) {
             float4 qv[4], kv[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int i = base + u * 128, tok = i / d4, r = (i - tok * d4) << 2;
+                const int i = base + u * THREADS, tok = i / d4, r = (i - tok * d4) << 2;
                 const int left = (i < RUN * d4 && tok < n) ? d - r : 0;
                 const float* src = p + (size_t)(t0 + tok) * row_stride + (size_t)h * d + r;
                 qv[u] = SUMS ? make_float4(0.0f, 0.0f, 0.0f, 0.0f) : take4<VEC>(src + q_col, left);
@@ -240,23 +241,23 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int i = base + u * 128, tok = i / d4, r = (i - tok * d4) << 2;
+                const int i = base + u * THREADS, tok = i / d4, r = (i - tok * d4) << 2;
                 if (i >= RUN * d4) break;
                 if (!SUMS) *reinterpret_cast<uint2*>(Qs + tok * QS + r) = pack4(act_silu ? silu4(qv[u]) : qv[u]);
                 *reinterpret_cast<uint2*>(Ks + tok * QS + r) = pack4(act_silu ? silu4(kv[u]) : kv[u]);
             }
         }
         {   // v: the rounded value, and the rounded value times g^(n-1-token) in two halves
-            float4 vv[RUN * CT / 4 / 128];
+            float4 vv[RUN * CT / 4 / THREADS];
 #pragma unroll
-            for (int u = 0; u < RUN * CT / 4 / 128; ++u) {
-                const int i = tid + u * 128, tok = i / (CT / 4), c = (i % (CT / 4)) << 2;
+            for (int u = 0; u < RUN * CT / 4 / THREADS; ++u) {
+                const int i = tid + u * THREADS, tok = i / (CT / 4), c = (i % (CT / 4)) << 2;
                 vv[u] = take4<VEC>(p + (size_t)(t0 + tok) * row_stride + v_col + (size_t)h * e + e0 + c,
                                    tok < n ? e - (e0 + c) : 0);
             }
 #pragma unroll
-            for (int u = 0; u < RUN * CT / 4 / 128; ++u) {
-                const int i = tid + u * 128, tok = i / (CT / 4), c = (i % (CT / 4)) << 2;
+            for (int u = 0; u < RUN * CT / 4 / THREADS; ++u) {
+                const int i = tid + u * THREADS, tok = i / (CT / 4), c = (i % (CT / 4)) << 2;
                 const uint2 packed = pack4(act_silu ? silu4(vv[u]) : vv[u]);
                 if (!SUMS) *reinterpret_cast<uint2*>(Vs + tok * VS + c) = packed;
                 const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&packed.x);
@@ -278,14 +279,15 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
         }
         __syncthreads();
 
-        const int row0 = warp * 16;                        // this warp's tokens of the run: row0 .. row0 + 15
+        // a warp owns 16 tokens of the run (row0 .. row0 + 15) and one half of the block's columns
+        const int band = warp & 3, row0 = band * 16, half_at = warp >> 2;
         // the address this lane gives to a transposing load of values: 16 tokens by 16 columns
         const int v_lane = (lane & 15) * VS + ((lane >> 4) << 3);
         if (!SUMS && row0 < n) {
             const __nv_bfloat16* qa = Qs + (row0 + g) * QS + 2 * t;
-            float acc[CT / 8][4];
+            float acc[2][4];
 #pragma unroll
-            for (int nt = 0; nt < CT / 8; ++nt)
+            for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[nt][j] = 0.0f;
             // what the state in front of the run gives: (q . S) g^(i+1)
@@ -293,22 +295,22 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
                 uint32_t a[4] = {ld32(qa + ks * 16), ld32(qa + 8 * QS + ks * 16), ld32(qa + ks * 16 + 8),
                                  ld32(qa + 8 * QS + ks * 16 + 8)};
 #pragma unroll
-                for (int nt = 0; nt < CT / 8; ++nt) {
-                    const int at = (nt * 8 + g) * QS + ks * 16 + 2 * t;
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int at = (half_at * 16 + nt * 8 + g) * QS + ks * 16 + 2 * t;
                     mma_bf16(acc[nt], a, ld32(SThi + at), ld32(SThi + at + 8));
                     mma_bf16(acc[nt], a, ld32(STlo + at), ld32(STlo + at + 8));
                 }
             }
             const float up = pw[row0 + g + 1], down = pw[row0 + g + 9];
 #pragma unroll
-            for (int nt = 0; nt < CT / 8; ++nt) {
+            for (int nt = 0; nt < 2; ++nt) {
                 acc[nt][0] *= up;
                 acc[nt][1] *= up;
                 acc[nt][2] *= down;
                 acc[nt][3] *= down;
             }
             // the run's own keys, 16 at a time up to this warp's last token: decayed scores, then P.V
-            for (int kk = 0; kk <= warp; ++kk) {
+            for (int kk = 0; kk <= band; ++kk) {
                 float sc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
                 for (int ks = 0; ks < dp16; ++ks) {
                     uint32_t a[4] = {ld32(qa + ks * 16), ld32(qa + 8 * QS + ks * 16), ld32(qa + ks * 16 + 8),
@@ -329,21 +331,18 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
                         const float w1 = j + 1 <= i ? sc[half][2 * rr + 1] * pw[i - j - 1] : 0.0f;
                         split_pair(w0, w1, ahi[2 * half + rr], alo[2 * half + rr]);
                     }
-#pragma unroll
-                for (int np = 0; np < CT / 16; ++np) {
-                    uint32_t b[4];
-                    ldsm4t(b, Vs + kk * 16 * VS + np * 16 + v_lane);
-                    mma_bf16(acc[2 * np], ahi, b[0], b[1]);
-                    mma_bf16(acc[2 * np], alo, b[0], b[1]);
-                    mma_bf16(acc[2 * np + 1], ahi, b[2], b[3]);
-                    mma_bf16(acc[2 * np + 1], alo, b[2], b[3]);
-                }
+                uint32_t b[4];
+                ldsm4t(b, Vs + kk * 16 * VS + half_at * 16 + v_lane);
+                mma_bf16(acc[0], ahi, b[0], b[1]);
+                mma_bf16(acc[0], alo, b[0], b[1]);
+                mma_bf16(acc[1], ahi, b[2], b[3]);
+                mma_bf16(acc[1], alo, b[2], b[3]);
             }
 #pragma unroll
-            for (int nt = 0; nt < CT / 8; ++nt)
+            for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int i = row0 + g + 8 * (j >> 1), c = e0 + nt * 8 + 2 * t + (j & 1);
+                    const int i = row0 + g + 8 * (j >> 1), c = e0 + half_at * 16 + nt * 8 + 2 * t + (j & 1);
                     if (i < n && c < e) o[(size_t)(t0 + i) * H * e + (size_t)h * e + c] = acc[nt][j];
                 }
         }
@@ -352,7 +351,7 @@ decay_runs_kernel(const float* __restrict__ p, long long row_stride, int q_col, 
         const int steps = (n + 15) >> 4;
         // this lane's address in a transposing load of keys: 16 tokens by 16 channels
         const int k_lane = ((lane & 7) + ((lane >> 4) << 3)) * QS + (((lane >> 3) & 1) << 3);
-        for (int mt = warp; mt < dp16; mt += 4) {
+        for (int mt = warp; mt < dp16; mt += THREADS / 32) {
             float* srow = Sf + (mt * 16 + g) * SF + 2 * t;
             float acc[CT / 8][4];
 #pragma unroll
@@ -487,7 +486,7 @@ FWB_API int fwb_decay_runs(const float* p, long long row_stride, int q_col, int 
         if (err != cudaSuccess) return (int)err;
     }
     if (chained) {
-        fwb::pdl(sums, dim3(P, H, tiles), 128, smem, stream)(
+        fwb::pdl(sums, dim3(P, H, tiles), THREADS, smem, stream)(
             p, row_stride, q_col, k_col, v_col, act_silu, decay, state, slot_stride, seg_start, seg_slot, piece_seg,
             piece_tok0, piece_len, scratch, o, H, d, e, DP);
         int status = fwb_launch_status();
@@ -497,7 +496,7 @@ FWB_API int fwb_decay_runs(const float* p, long long row_stride, int q_col, int 
         status = fwb_launch_status();
         if (status != FWB_OK) return status;
     }
-    fwb::pdl(walk, dim3(P, H, tiles), 128, smem, stream)(
+    fwb::pdl(walk, dim3(P, H, tiles), THREADS, smem, stream)(
         p, row_stride, q_col, k_col, v_col, act_silu, decay, state, slot_stride, seg_start, seg_slot, piece_seg,
         piece_tok0, piece_len, chained ? scratch : nullptr, o, H, d, e, DP);
     return fwb_launch_status();

@@ -195,6 +195,32 @@ def run_delta_rule(args) -> dict:
             "gb_s": (state_bytes + stream_bytes) / us / 1e3, "gflops": 6.0 * T * H * d * e / us / 1e3}
 
 
+def run_linear_attention(args) -> dict:
+    """The decayed linear recurrence over ``batch`` segments of ``tokens`` tokens: token by token
+    (``--scan``) or 64 tokens at a time on tensor cores."""
+    from ..engine.batch import Segment, StepBatch
+    from . import mixing
+    H, d, e = args.heads, args.dim, args.vdim
+    dev = torch.device("cuda", 0)
+    T = args.batch * args.tokens
+    g = torch.Generator(device=dev).manual_seed(0)
+    p = torch.randn((T, 2 * H * d + 2 * H * e), generator=g, device=dev, dtype=torch.float32)
+    decay = torch.linspace(0.9, 0.999, H, device=dev, dtype=torch.float32)
+    state = torch.zeros((args.batch, H * d * e), device=dev, dtype=torch.float32)
+    batch = StepBatch([Segment(f"r{i}", i, 0, [0] * args.tokens, []) for i in range(args.batch)],
+                      [[[0]] * args.batch], dev)
+    kernel = mixing.decay_scan if args.scan else mixing.decay_runs
+
+    def step():
+        kernel(p, 0, H * d, 2 * H * d, decay, state, batch, H, d, e, act_silu=True)
+
+    us = _time(step, args.repeat)
+    stream_bytes = T * (2 * H * d + 2 * H * e) * 4 + 2 * args.batch * H * d * e * 4
+    return {"kernel": "decay_scan" if args.scan else "decay_runs", "batch": args.batch, "tokens": args.tokens,
+            "heads": H, "dim": d, "vdim": e, "us": us, "gb_s": stream_bytes / us / 1e3,
+            "gflops": 4.0 * T * H * d * e / us / 1e3}
+
+
 def run_qk_norm_rope(args) -> dict:
     from . import ops
     T, nh, nkv, hd = args.tokens, args.heads, args.kv_heads, args.head_dim
@@ -311,6 +337,13 @@ def main(argv=None) -> int:
     delta.add_argument("--vdim", type=int, default=128)
     delta.add_argument("--taps", type=int, default=4)
     delta.add_argument("--graph", action="store_true")
+    lin = sub.add_parser("linear-attention")
+    lin.add_argument("--batch", type=int, default=1)
+    lin.add_argument("--tokens", type=int, default=2048)
+    lin.add_argument("--heads", type=int, default=16)
+    lin.add_argument("--dim", type=int, default=128)
+    lin.add_argument("--vdim", type=int, default=128)
+    lin.add_argument("--scan", action="store_true", help="the token-by-token kernel")
     smp = sub.add_parser("sample")
     smp.add_argument("--rows", type=int, default=8)
     smp.add_argument("--vocab", type=int, default=65536)
@@ -324,7 +357,8 @@ def main(argv=None) -> int:
     args = parser.parse_args(argv)
     runner = {"gemm": run_gemm, "attention-decode": run_attention_decode,
               "attention-prefill": run_attention_prefill, "shortconv": run_shortconv,
-              "qk-norm-rope": run_qk_norm_rope, "sample": run_sample, "delta-rule": run_delta_rule}[args.kernel]
+              "qk-norm-rope": run_qk_norm_rope, "sample": run_sample, "delta-rule": run_delta_rule,
+              "linear-attention": run_linear_attention}[args.kernel]
     print(json.dumps(runner(args)))
     return 0
 
