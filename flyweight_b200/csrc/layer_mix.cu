@@ -101,6 +101,21 @@ __global__ void unary_act_kernel(const TI* __restrict__ in, TO* __restrict__ out
         out[i] = from_f32<TO>(unary_f32(to_f32<TI>(in[i]), act));
 }
 
+// bfloat16 to bfloat16, eight entries (16 bytes) a thread and turn
+__global__ void unary_act_bf16x8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, size_t groups, int act) {
+    fwb::pdl_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (size_t)gridDim.x * blockDim.x) {
+        uint4 v = in[i];
+        __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(pair[j]);
+            pair[j] = __floats2bfloat162_rn(unary_f32(f.x, act), unary_f32(f.y, act));
+        }
+        out[i] = v;
+    }
+}
+
 template <typename TI, typename TT, typename TO>
 __global__ void side_gate_kernel(const TI* __restrict__ g, const TT* __restrict__ table, int table_width, int col0,
                                  const int* __restrict__ tokens, int vocab, TO* __restrict__ out, int n_rows, int dim) {
@@ -212,7 +227,9 @@ FWB_API int fwb_unary_act(const void* in, int in_bf16, void* out, int out_bf16, 
     if (n <= 0) return FWB_OK;
     if (!in || !out || act < 0 || act > 3) return FWB_BAD_ARGUMENT;
     const int blocks = blocks_for((size_t)n);
-    if (in_bf16 && out_bf16) fwb::pdl(unary_act_kernel<bf, bf>, blocks, 256, 0, stream)((const bf*)in, (bf*)out, (size_t)n, act);
+    if (in_bf16 && out_bf16 && n % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0)
+        fwb::pdl(unary_act_bf16x8_kernel, blocks_for((size_t)n / 8), 256, 0, stream)((const uint4*)in, (uint4*)out, (size_t)n / 8, act);
+    else if (in_bf16 && out_bf16) fwb::pdl(unary_act_kernel<bf, bf>, blocks, 256, 0, stream)((const bf*)in, (bf*)out, (size_t)n, act);
     else if (!in_bf16 && out_bf16) fwb::pdl(unary_act_kernel<float, bf>, blocks, 256, 0, stream)((const float*)in, (bf*)out, (size_t)n, act);
     else if (!in_bf16 && !out_bf16) fwb::pdl(unary_act_kernel<float, float>, blocks, 256, 0, stream)((const float*)in, (float*)out, (size_t)n, act);
     else return FWB_UNSUPPORTED;

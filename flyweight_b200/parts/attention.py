@@ -92,9 +92,10 @@ class GQAttention(Mixer):
         # the launches LFM2 makes: nothing of the above, so the fused decode kernel and the native plan apply
         self._plain = not (self.has_sink or self.softcap or self.gate or self.value_mix
                            or self.qk_norm == "whole" or (self.head_dim != self.qk_dim and self.eps is not None))
-        # q|k|v leave their product in fp32 when another kernel works on them before the head kernel
-        # reads them (a norm over the whole projection, values mixed in place): one rounding, not two
-        self._wide_qkv = self.qk_norm == "whole" or self.value_mix is not None
+        # q|k|v leave their product in fp32 when a norm over the whole projection works on them in place before
+        # the head kernel reads them: one rounding, not two.  (Mixed values are rounded on both sides of the
+        # mix in 16-bit runs: what the products' dtype means for a projection and for a cached value.)
+        self._wide_qkv = self.qk_norm == "whole"
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.w_gate = self.sink = self.vmix = None
 
     @property

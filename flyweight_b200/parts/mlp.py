@@ -42,5 +42,6 @@ class DenseMLP(FeedForward):
         act = ctx.precision.act_dtype
         if not isinstance(h, torch.Tensor):
             h = h.materialize(act)
-        a = mixing.unary_act(ops.linear(h, self.w_up, torch.float32), self.activation, act)
+        # (the hidden row leaves its product in the products' dtype; the activation itself is computed in fp32)
+        a = mixing.unary_act(ops.linear(h, self.w_up, act), self.activation, act)
         return ops.linear(a, self.w_down, torch.float32)
