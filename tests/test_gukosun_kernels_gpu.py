@@ -50,10 +50,13 @@ CUTS_LONG = [[(0, 300), (1, 1), (2, 70)], [(1, 1), (0, 17), (3, 2)], [(0, 1), (1
 
 
 @pytest.mark.parametrize("form", ["scan", "runs"])
-@pytest.mark.parametrize("H,d,e", [(2, 16, 8), (3, 24, 40), (1, 128, 128), (2, 64, 32), (1, 1, 1)])
-def test_decayed_recurrence_over_portions_pieces_and_single_tokens(form, H, d, e):
+@pytest.mark.parametrize("pad", [5, 8])
+@pytest.mark.parametrize("H,d,e", [(2, 16, 8), (3, 24, 40), (1, 128, 128), (2, 64, 32), (1, 1, 1), (2, 18, 10)])
+def test_decayed_recurrence_over_portions_pieces_and_single_tokens(form, pad, H, d, e):
     """Four sequences in shuffled slots, fed in portions of 1 to 700 tokens (shorter and longer than a run of
-    64 and a piece of 256, and ending on their borders), from a state that is not zero."""
+    64 and a piece of 256, and ending on their borders), from a state that is not zero.  ``pad``: unused
+    columns behind the projections (5: rows that start off every 16-byte border, so the kernel loads entry by
+    entry; 8: rows that 16-byte loads can take where the head sizes allow)."""
     from flyweight_b200.kernels import mixing
     g = torch.Generator().manual_seed(H * 100 + d)
     lengths = [0, 0, 0, 0]
@@ -61,7 +64,7 @@ def test_decayed_recurrence_over_portions_pieces_and_single_tokens(form, H, d, e
         for s, m in step:
             lengths[s] += m
     decay = torch.tensor([1.0 - 2.0 ** (-2 - 3 * j) for j in range(H)], dtype=F64)
-    width = 2 * H * d + H * e + 5                       # (columns behind the three that the kernel does not read)
+    width = 2 * H * d + H * e + pad
     rows = [torch.randn(n, width, generator=g, dtype=F64).float().to(F64) for n in lengths]
     slots = [2, 0, 3, 1]
     start = torch.randn(4, H, d, e, generator=g, dtype=F64).float().to(F64)
