@@ -18,6 +18,12 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* src, float (&f)[8]) {
     }
 }
 
+__device__ __forceinline__ void load8(const float* src, float (&f)[8]) {
+    const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+    f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w;
+    f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+}
+
 __device__ __forceinline__ void store8(__nv_bfloat16* dst, const float (&f)[8]) {
     uint4 out;
     __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&out);

@@ -130,8 +130,10 @@ qk_norm_rope_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
 // load and store per lane), so a warp works on 32/(hd/8) heads at a time.  The sum of squares
 // goes over the lanes of a head in lane order; the rotation partner (i +- rot/2) sits
 // rot/16 lanes away and is fetched with shuffles.  Needs hd % 8 == 0, hd <= 256, rot % 16 == 0.
+// TI: the projection's type (bfloat16, or fp32 rows that another kernel has worked on in place).
+template <typename TI>
 __global__ void __launch_bounds__(WARPS * 32)
-qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ wq,
+qk_norm_rope_bf16x8_kernel(const TI* __restrict__ qkv, const float* __restrict__ wq,
                            const float* __restrict__ wk, const float2* __restrict__ table,
                            const int* __restrict__ positions, const int* __restrict__ tok_seg,
                            const int* __restrict__ block_table, int max_pages, int page_size,
@@ -145,7 +147,7 @@ qk_norm_rope_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float* _
     const int sub = lane / G, gl = lane - sub * G;
     const int pos = positions[t];
     const int heads = nh + 2 * nkv;
-    const __nv_bfloat16* row = qkv + (size_t)t * heads * hd;
+    const TI* row = qkv + (size_t)t * heads * hd;
     const float2* cs = table + (size_t)pos * (rot / 2);
     size_t cache_base = 0;
     if (nkv > 0) {
@@ -213,13 +215,19 @@ FWB_API int fwb_qk_norm_rope_ordered(const void* qkv, int in_bf16, const float* 
         page_size, (TQ*)q_out, (TC*)k_pool, (TC*)v_pool, nh, nkv, hd, rot, eps, use_norm, pairing, norm_dim)
     const int key = (in_bf16 ? 4 : 0) | (q_bf16 ? 2 : 0) | (cache_bf16 ? 1 : 0);
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
-    if (key == 7 && (hd & 7) == 0 && hd <= 256 && (rot & 15) == 0 && aligned) {
+    if ((key == 7 || key == 3) && (hd & 7) == 0 && hd <= 256 && (rot & 15) == 0 && aligned) {
         const int per_block = WARPS * (32 / (hd >> 3));
         const dim3 vgrid(T, T >= 256 ? 1 : (nh + 2 * nkv + per_block - 1) / per_block);
-        fwb::pdl(qk_norm_rope_bf16x8_kernel, vgrid, WARPS * 32, 0, stream)(
-            (const __nv_bfloat16*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table,
-            max_pages, page_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh,
-            nkv, hd, rot, eps, use_norm, pairing, norm_dim);
+        if (key == 7)
+            fwb::pdl(qk_norm_rope_bf16x8_kernel<__nv_bfloat16>, vgrid, WARPS * 32, 0, stream)(
+                (const __nv_bfloat16*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table,
+                max_pages, page_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh,
+                nkv, hd, rot, eps, use_norm, pairing, norm_dim);
+        else
+            fwb::pdl(qk_norm_rope_bf16x8_kernel<float>, vgrid, WARPS * 32, 0, stream)(
+                (const float*)qkv, wq, wk, (const float2*)table, positions, tok_seg, block_table,
+                max_pages, page_size, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, nh,
+                nkv, hd, rot, eps, use_norm, pairing, norm_dim);
         return fwb_launch_status();
     }
     switch (key) {
