@@ -7,7 +7,7 @@
 //                           not count)
 //   fwb_value_mix:          save: first[t][:] = rows[t][c0 .. c0+n);  mix: rows[t][c0+i] <- (1-lam) rows + lam first
 //   fwb_sigmoid_gate_mul:   y[t][h][c] *= sigmoid(gate[t][h*gw + (gw == 1 ? 0 : c)])
-//   fwb_scaled_add:         x[t][c] += s1[c] a[t][c] (+ s2[c] b[t][c])                        (fp32)
+//   fwb_scaled_add:         x[t][c] += s1[c] a[t][c] (+ s2[c] b[t][c])                        (fp32; a bf16 copy on request)
 //   fwb_unary_act:          out = act(in), act = relu squared | silu | sigmoid | gelu (tanh form)
 //   fwb_side_gate:          out[t][c] = gelu(g[t][c]) * table[token[t]][c0 + c]
 //   fwb_scale:              x *= s                                                            (fp32)
@@ -74,14 +74,17 @@ __global__ void sigmoid_gate_mul_kernel(T* __restrict__ y, const T* __restrict__
 }
 
 __global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ s1,
-                                  const float* __restrict__ b, const float* __restrict__ s2, int n_rows, int H) {
+                                  const float* __restrict__ b, const float* __restrict__ s2, __nv_bfloat16* __restrict__ copy,
+                                  int n_rows, int H) {
     fwb::pdl_entry();
     const size_t n = (size_t)n_rows * H;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const int c = (int)(i % H);
         float d = (s1 ? s1[c] : 1.0f) * a[i];
         if (b) d += (s2 ? s2[c] : 1.0f) * b[i];
-        x[i] += d;
+        const float sum = x[i] + d;
+        x[i] = sum;
+        if (copy) copy[i] = __float2bfloat16_rn(sum);
     }
 }
 
@@ -213,12 +216,13 @@ FWB_API int fwb_sigmoid_gate_mul(void* y, const void* gate, int is_bf16, int T, 
     return fwb_launch_status();
 }
 
-// x, a, b: [T][H] fp32 (b may be null); s1, s2: [H] fp32 or null (no scale).
-FWB_API int fwb_scaled_add(float* x, const float* a, const float* s1, const float* b, const float* s2, int T, int H,
-                           cudaStream_t stream) {
+// x, a, b: [T][H] fp32 (b may be null); s1, s2: [H] fp32 or null (no scale); copy_bf16: [T][H] bfloat16 or null
+// (the new stream once more, rounded, for a product that reads it next).
+FWB_API int fwb_scaled_add(float* x, const float* a, const float* s1, const float* b, const float* s2, void* copy_bf16,
+                           int T, int H, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!x || !a || H <= 0) return FWB_BAD_ARGUMENT;
-    fwb::pdl(scaled_add_kernel, blocks_for((size_t)T * H), 256, 0, stream)(x, a, s1, b, s2, T, H);
+    fwb::pdl(scaled_add_kernel, blocks_for((size_t)T * H), 256, 0, stream)(x, a, s1, b, s2, (__nv_bfloat16*)copy_bf16, T, H);
     return fwb_launch_status();
 }
 

@@ -75,8 +75,11 @@ def sigmoid_gate_mul_(y: torch.Tensor, gate: torch.Tensor, heads: int, head_dim:
 
 
 def scaled_add_(x: torch.Tensor, a: torch.Tensor, scale_a: Optional[torch.Tensor],
-                b: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None) -> None:
-    """``x += scale_a * a (+ scale_b * b)`` per channel, in place and in fp32 (a scale may be None: 1)."""
+                b: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None,
+                copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """``x += scale_a * a (+ scale_b * b)`` per channel, in place and in fp32 (a scale may be None: 1).
+    ``copy_dtype`` bfloat16: also returns the new ``x`` rounded to bfloat16 (what a product that reads the
+    stream next takes), written in the same pass; any other value returns None."""
     check_tensor("residual", x, torch.float32)
     H = x.shape[-1]
     check_tensor("sublayer output", a, torch.float32, x.shape)
@@ -85,7 +88,10 @@ def scaled_add_(x: torch.Tensor, a: torch.Tensor, scale_a: Optional[torch.Tensor
             check_tensor(name, t, torch.float32, (H,))
     if b is not None:
         check_tensor("second sublayer output", b, torch.float32, x.shape)
-    lib.call("fwb_scaled_add", ptr(x), ptr(a), ptr(scale_a), ptr(b), ptr(scale_b), x.numel() // H, H, stream())
+    copy = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if copy_dtype == torch.bfloat16 else None
+    lib.call("fwb_scaled_add", ptr(x), ptr(a), ptr(scale_a), ptr(b), ptr(scale_b), ptr(copy), x.numel() // H, H,
+             stream())
+    return copy
 
 
 def unary_act(x: torch.Tensor, activation: str, out_dtype: torch.dtype) -> torch.Tensor:

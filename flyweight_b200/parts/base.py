@@ -267,8 +267,9 @@ class StreamShift(Part):
 class SideInput(Part):
     """Something a layer adds into the residual stream from the step's token ids, behind its sublayers."""
 
-    def forward(self, ctx, x):
-        """Adds into the fp32 stream ``x`` in place."""
+    def forward(self, ctx, x, x_act=None):
+        """Adds into the fp32 stream ``x`` in place.  ``x_act``: the same rows in the products' dtype, if the
+        caller has them already."""
         raise NotImplementedError
 
 

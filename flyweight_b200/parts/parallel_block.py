@@ -26,8 +26,10 @@ class ParallelResidual(Arrangement):
         h = self.norm.forward(ctx, x, delta=pending)
         y = self.mixer.forward(ctx, h, cache)
         f = self.feed_forward.forward(ctx, h) if self.feed_forward is not None else None
-        mixing.scaled_add_(x, y, None if self.mixer_scale is None else self.mixer_scale.weight,
-                           f, None if self.ffn_scale is None else self.ffn_scale.weight)
+        # (the side input's first product reads the new stream in the products' dtype: the sum writes that copy too)
+        rounded = mixing.scaled_add_(x, y, None if self.mixer_scale is None else self.mixer_scale.weight,
+                                     f, None if self.ffn_scale is None else self.ffn_scale.weight,
+                                     copy_dtype=ctx.precision.act_dtype if self.side is not None else None)
         if self.side is not None:
-            self.side.forward(ctx, x)
+            self.side.forward(ctx, x, rounded)
         return x, None

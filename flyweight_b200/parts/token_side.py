@@ -56,9 +56,9 @@ class TokenSideInput(SideInput):
     def flops_per_token(self):
         return 2.0 * (self.w_gate.numel() + self.w_proj.numel())
 
-    def forward(self, ctx, x):
+    def forward(self, ctx, x, x_act=None):
         act = ctx.precision.act_dtype
-        g = ops.linear(ops.cast(x, act), self.w_gate, torch.float32)
+        g = ops.linear(x_act if x_act is not None else ops.cast(x, act), self.w_gate, torch.float32)
         a = mixing.side_gate(g, self.table, 0, ctx.batch.token_ids, act)
         y = ops.linear(a, self.w_proj, torch.float32)
         ops.rmsnorm_add_(x, y, self.norm, self.eps)
