@@ -208,3 +208,58 @@ def test_the_model_folder_round_trip_the_command_line_and_the_trace_runner(tmp_p
     assert not (tmp_path / "out" / "1.f32").exists()
     got = np.fromfile(tmp_path / "out" / "2.f32", dtype="<f4").reshape(1, -1)
     assert_close(got, want[[74]], TOL_ORACLE["float32"], "step 2")
+
+
+# ------------------------------------------------------------------ wider layers, longer prompts
+def _wider_config(v):
+    if v == 0:
+        att = {"heads": 4, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.11, "mask": {"size": 100}, "v_mix": True}
+        att_nomix = {"heads": 6, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.2, "mask": {"size": 300}}
+        left = {"heads": 8, "kv_heads": 1, "dim": 64, "vdim": 32, "scale": 0.125,
+                "rot": {"base": 10000.0, "dims": 32}}
+        right = {"heads": 2, "dim": 64, "vdim": 96, "decay": [0.99, 0.9]}
+        mlp = {"kind": "dense", "ff": 384}
+        layers = [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp},
+                  {"type": "attention", "mixer": att, "mlp": None},
+                  {"type": "attention", "mixer": att_nomix, "mlp": mlp},
+                  {"type": "attention", "mixer": att, "mlp": mlp},
+                  {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": None},
+                  {"type": "attention", "mixer": att, "mlp": mlp}]
+        return {"architecture": "Gukosun", "vocab": 1000, "width": 256, "norm": {"eps": 1e-6}, "layers": layers}
+    att = {"heads": 12, "kv_heads": 3, "dim": 128, "vdim": 64, "scale": 0.09, "mask": {"size": 257}, "v_mix": True}
+    left = {"heads": 4, "kv_heads": 2, "dim": 80, "vdim": 80, "scale": 0.1, "softcap": 50.0,
+            "rot": {"base": 500000.0, "dims": 80, "scaling": {"factor": 32.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    right = {"heads": 5, "dim": 24, "vdim": 56, "decay": [0.5, 0.8, 0.95, 0.99, 0.999]}
+    mlp = {"kind": "dense", "ff": 700}
+    layers = [{"type": "attention", "mixer": att, "mlp": mlp},
+              {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp},
+              {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp},
+              {"type": "attention", "mixer": att, "mlp": mlp}]
+    return {"architecture": "Gukosun", "vocab": 777, "width": 320, "norm": {"eps": 1e-5}, "logit_scale": 3.0,
+            "token_side": {"dim": 24}, "layers": layers}
+
+
+@pytest.mark.parametrize("variant", (0, 1))
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_wider_layers_and_prompts_longer_than_a_piece_of_the_recurrence(variant, dtype, tmp_path):
+    """Two configurations with heads of 24 to 128 channels (values wider than keys and narrower, one KV head and
+    as many as query heads, 80-channel heads, rotation of half a head and of a whole one, no cap, no frequency
+    scaling, no side input, layers without a feed-forward, a layer that mixes no values between two that do):
+    700 tokens whole, in portions that end on and off the borders of pages, windows and the recurrence's
+    pieces of 256, and as a prompt of 600 followed by 100 single tokens."""
+    from tiny_configs import make_model_dir
+    from flyweight_b200.engine import ModelRunner, load_model
+    config = _wider_config(variant)
+    stored = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = make_model_dir(str(tmp_path / "model"), config, seed=7 + variant, dtype=stored)
+    cfg, w = P.load_model_dir(folder)
+    rng = np.random.default_rng(variant)
+    tokens = [int(t) for t in rng.integers(0, config["vocab"], size=700)]
+    rnd = (lambda t: t.to(torch.bfloat16).to(torch.float64)) if dtype == "bfloat16" else (lambda t: t)
+    want = np.asarray(P.forward(cfg, w, tokens, rnd=rnd))
+    runner = ModelRunner(load_model(folder, dtype), num_pages=16, num_slots=4, max_model_len=1024,
+                         max_batched_tokens=4096)
+    for what, sizes in (("whole", [700]), ("portions", [300, 2, 1, 257, 64, 1, 1, 74]), ("decoding", [600] + [1] * 100)):
+        assert_close(run_portions(runner, what, tokens, sizes), want, 2e-4 if dtype == "float32" else 4e-2,
+                     f"variant {variant} {dtype} {what}")
+    runner.check_health()
