@@ -72,6 +72,9 @@ class ScheduleEntry:
     """
     layer: int
     cache_of: Optional[int] = None
+    # True: what the embedding made of the step's tokens is added to the stream once more right in front
+    # of this execution (a model that runs a run of layers several times feeds its input to every pass)
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

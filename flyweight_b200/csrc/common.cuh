@@ -142,4 +142,21 @@ __device__ __forceinline__ float silu_f32(float g) {
     return g * sig;
 }
 
+// What a gated feed-forward makes of a gate value g and an up value u.  0: silu(g) u.  1: gelu(g) u (tanh
+// form).  2, the clamped swish: g is cut off above `limit`, u is held inside [-limit, limit], and the
+// result is g sigmoid(1.702 g) (u + 1).
+constexpr int GATED_SILU = 0, GATED_GELU_TANH = 1, GATED_SWISH_CLAMPED = 2;
+constexpr float SWISH_CLAMPED_SLOPE = 1.702f;
+__device__ __forceinline__ float gated_f32(int act, float limit, float g, float u) {
+    if (act == GATED_SWISH_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        const float z = SWISH_CLAMPED_SLOPE * g;
+        const float e = expf(-fabsf(z));
+        const float sig = z >= 0.0f ? 1.0f / (1.0f + e) : e / (1.0f + e);
+        return g * sig * (u + 1.0f);
+    }
+    return (act == GATED_GELU_TANH ? gelu_tanh_f32(g) : silu_f32(g)) * u;
+}
+
 }  // namespace fwb

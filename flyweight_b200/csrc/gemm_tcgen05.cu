@@ -104,7 +104,8 @@ struct Params {
     int M, N, K;           // tokens, features (of one accumulator), reduction
     int ldy;
     int up_row_offset;     // SwiGLU: rows of the up projection start here in W
-    int gate_act;          // SwiGLU: the gate's activation (tc5 GATE_SILU | GATE_GELU_TANH)
+    int gate_act;          // SwiGLU: the gate's activation (tc5 GATE_SILU | GATE_GELU_TANH | GATE_SWISH_CLAMPED)
+    float gate_limit;      // the clamped swish's limit
     int k_blocks_per_split;
     int stages;            // depth of the shared-memory ring (<= Tile::MAX_STAGES)
     int* status;           // the library's status word (see tc5::status_word)
@@ -376,7 +377,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (f + BM < prm.N) reinterpret_cast<__nv_bfloat16*>(prm.y)[at + BM] = __float2bfloat16_rn(u);
         } else if (EPI == EPI_ADD_F32) reinterpret_cast<float*>(prm.y)[at] = g + (splits > 1 ? u : prm.addend[at]);
         else if (EPI == EPI_BF16) reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(g);
-        else reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(gate_act_fast(prm.gate_act, g) * u);
+        else reinterpret_cast<__nv_bfloat16*>(prm.y)[at] = __float2bfloat16_rn(gated_fast(prm.gate_act, prm.gate_limit, g, u));
     };
 
     if (splits == 1) {
@@ -547,7 +548,7 @@ int launch_epi(int epi, const CUtensorMap& map_w, const CUtensorMap& map_x, cons
 // pointers 16-byte aligned; anything else is refused.
 FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float* addend, int M, int N,
                              int K, int w_rows, int ldy, int epilogue, int up_row_offset, int splits,
-                             int stages, int tile_tokens, int wide, cudaStream_t stream) {
+                             int stages, int tile_tokens, int wide, float gate_limit, cudaStream_t stream) {
     const int gate_act = epilogue >> 8;     // bits above the epilogue code: the gate's activation
     epilogue &= 0xff;
     if (M <= 0 || N <= 0) return FWB_OK;
@@ -589,6 +590,7 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
     prm.ldy = ldy;
     prm.up_row_offset = up_row_offset;
     prm.gate_act = gate_act;
+    prm.gate_limit = gate_limit;
     prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
     prm.stages = stages;
     prm.status = status_word();
@@ -619,7 +621,7 @@ FWB_API int fwb_gemm_tcgen05(const void* X, const void* W, void* Y, const float*
 FWB_API int fwb_gemm_tcgen05_normed(const float* x_res, const float* norm_w, const int* rows, float eps,
                                     const void* W, void* Y, int M, int N, int K, int w_rows, int ldy,
                                     int epilogue, int up_row_offset, int splits, int stages,
-                                    int tile_tokens, cudaStream_t stream) {
+                                    int tile_tokens, float gate_limit, cudaStream_t stream) {
     const int gate_act = epilogue >> 8;
     epilogue &= 0xff;
     if (M <= 0 || N <= 0) return FWB_OK;
@@ -646,6 +648,7 @@ FWB_API int fwb_gemm_tcgen05_normed(const float* x_res, const float* norm_w, con
     prm.ldy = ldy;
     prm.up_row_offset = up_row_offset;
     prm.gate_act = gate_act;
+    prm.gate_limit = gate_limit;
     prm.k_blocks_per_split = (total_kb + splits - 1) / splits;
     prm.stages = stages;
     prm.status = status_word();
@@ -723,7 +726,7 @@ FWB_API int fwb_set_pdl(int enabled) {
 FWB_API int fwb_gemm_tcgen05_grouped(const void* X, const void* W, void* Y, const int* offsets, const int* tiles,
                                      int max_tiles, int tile_rows, int A, int N, int K, int n_groups,
                                      int group_w_rows, int ldy, int epilogue, int up_row_offset,
-                                     cudaStream_t stream) {
+                                     float gate_limit, cudaStream_t stream) {
     const int gate_act = epilogue >> 8;
     epilogue &= 0xff;
     if (A <= 0 || N <= 0 || max_tiles <= 0 || n_groups <= 0) return FWB_OK;
@@ -748,6 +751,7 @@ FWB_API int fwb_gemm_tcgen05_grouped(const void* X, const void* W, void* Y, cons
     prm.ldy = ldy;
     prm.up_row_offset = up_row_offset;
     prm.gate_act = gate_act;
+    prm.gate_limit = gate_limit;
     prm.k_blocks_per_split = (K + BK - 1) / BK;
     prm.stages = 0;
     prm.status = status_word();

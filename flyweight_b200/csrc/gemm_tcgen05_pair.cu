@@ -288,6 +288,7 @@ FWB_API int fwb_gemm_tcgen05_pair(const void* X, const void* W, void* Y, int M, 
                                   int ldy, int epilogue, int up_row_offset, int wide, cudaStream_t stream) {
     const int gate_act = epilogue >> 8;     // bits above the epilogue code: the gate's activation
     epilogue &= 0xff;
+    if (gate_act > GATE_GELU_TANH) return FWB_UNSUPPORTED;     // (activations with a parameter: the one-CTA kernel)
     if (M <= 0 || N <= 0) return FWB_OK;
     if (!X || !W || !Y || K <= 0 || ldy < N) return FWB_BAD_ARGUMENT;
     if ((K & 7) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return FWB_UNSUPPORTED;

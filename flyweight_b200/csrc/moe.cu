@@ -193,6 +193,20 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ router, con
     }
 }
 
+// A router that is a table: token id -> its `top` experts, each with weight 1 / top.
+__global__ void __launch_bounds__(256)
+moe_route_table_kernel(const int* __restrict__ token_ids, const int* __restrict__ table, int vocab, int top, int T,
+                       int* __restrict__ ids, float* __restrict__ weights) {
+    fwb::pdl_entry();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * top) return;
+    const int t = i / top, slot = i - t * top;
+    int token = token_ids[t];
+    token = token < 0 ? 0 : (token >= vocab ? vocab - 1 : token);   // (the embedding flags such an id)
+    ids[i] = table[(size_t)token * top + slot];
+    weights[i] = 1.0f / (float)top;
+}
+
 // One block.  ids: [A] router outputs of the pairs (A = tokens * top).  Writes
 //   offsets[E + 1]   first row of every expert among the sorted rows
 //   row_token[A]     token of every sorted row
@@ -257,7 +271,7 @@ template <typename TX, typename TW, typename TO, int FORM>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                 const int* __restrict__ offsets, const int* __restrict__ row_token, const int* __restrict__ tiles,
-                int N, int K, int act) {
+                int N, int K, int act, float limit) {
     fwb::pdl_entry();
     const int tile = blockIdx.y;
     if (tile >= tiles[0]) return;
@@ -318,7 +332,7 @@ moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restri
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             float v = acc[i][j];
-            if (FORM) v = (act == 1 ? gelu_tanh_f32(v) : silu_f32(v)) * acc2[i][j];
+            if (FORM) v = gated_f32(act, limit, v, acc2[i][j]);
             out[(size_t)row * N + n] = from_f32<TO>(v);
         }
     }
@@ -489,6 +503,15 @@ FWB_API int fwb_moe_route(const void* h, int h_bf16, const float* router, const 
     return fwb_launch_status();
 }
 
+// token_ids: [T] int32; table: [vocab][top] int32; ids, weights: [T][top].
+FWB_API int fwb_moe_route_table(const int* token_ids, const int* table, int vocab, int top, int T, int* ids,
+                                float* weights, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!token_ids || !table || !ids || !weights || vocab <= 0 || top <= 0) return FWB_BAD_ARGUMENT;
+    fwb::pdl(moe_route_table_kernel, (T * top + 255) / 256, 256, 0, stream)(token_ids, table, vocab, top, T, ids, weights);
+    return fwb_launch_status();
+}
+
 // ids: [A]; offsets: [E + 1]; row_token, pair_row: [A]; tiles: [1 + 2 (A / tile_rows + E + 1)].
 // tile_rows: rows of a tile of the products that follow (TM = 64 for fwb_moe_gemm).
 FWB_API int fwb_moe_sort(const int* ids, int A, int top, int E, int tile_rows, int* offsets, int* row_token,
@@ -517,26 +540,26 @@ FWB_API int fwb_moe_gather_rows(const void* h, const int* row_token, const int* 
 // x and w are both fp32 or both bf16.  max_tiles: the most tiles the sorted list can hold (the grid).
 FWB_API int fwb_moe_gemm(const void* x, const void* w, int bf16, void* out, const int* offsets,
                          const int* row_token, const int* tiles, int max_tiles, int N, int K, int form, int act,
-                         cudaStream_t stream) {
+                         float limit, cudaStream_t stream) {
     if (max_tiles <= 0) return FWB_OK;
     if (!x || !w || !out || !offsets || !row_token || !tiles || N <= 0 || K <= 0 || form < 0 || form > 1 ||
-        act < 0 || act > 1)
+        act < 0 || act > 2)
         return FWB_BAD_ARGUMENT;
     if (max_tiles > 65535) return FWB_TOO_LARGE;
     const dim3 grid((N + TN - 1) / TN, max_tiles);
     using bf = __nv_bfloat16;
     if (form == 1 && bf16)
         fwb::pdl(moe_gemm_kernel<bf, bf, bf, 1>, grid, 256, 0, stream)((const bf*)x, (const bf*)w, (bf*)out, offsets,
-                                                                       row_token, tiles, N, K, act);
+                                                                       row_token, tiles, N, K, act, limit);
     else if (form == 1)
         fwb::pdl(moe_gemm_kernel<float, float, float, 1>, grid, 256, 0, stream)(
-            (const float*)x, (const float*)w, (float*)out, offsets, row_token, tiles, N, K, act);
+            (const float*)x, (const float*)w, (float*)out, offsets, row_token, tiles, N, K, act, limit);
     else if (bf16)
         fwb::pdl(moe_gemm_kernel<bf, bf, float, 0>, grid, 256, 0, stream)((const bf*)x, (const bf*)w, (float*)out,
-                                                                          offsets, row_token, tiles, N, K, act);
+                                                                          offsets, row_token, tiles, N, K, act, limit);
     else
         fwb::pdl(moe_gemm_kernel<float, float, float, 0>, grid, 256, 0, stream)(
-            (const float*)x, (const float*)w, (float*)out, offsets, row_token, tiles, N, K, act);
+            (const float*)x, (const float*)w, (float*)out, offsets, row_token, tiles, N, K, act, limit);
     return fwb_launch_status();
 }
 

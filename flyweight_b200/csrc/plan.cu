@@ -31,9 +31,9 @@ int fwb_patch_tokens(int*, const int*, const int*, const int*, int, cudaStream_t
 int fwb_gemm_simt(const void*, int, const void*, int, void*, int, const float*, int, int, int, int, int,
                   cudaStream_t);
 int fwb_gemm_tcgen05(const void*, const void*, void*, const float*, int, int, int, int, int, int, int, int,
-                     int, int, int, cudaStream_t);
+                     int, int, int, float, cudaStream_t);
 int fwb_gemm_tcgen05_normed(const float*, const float*, const int*, float, const void*, void*, int, int, int,
-                            int, int, int, int, int, int, int, cudaStream_t);
+                            int, int, int, int, int, int, int, float, cudaStream_t);
 int fwb_gemm_tcgen05_pair(const void*, const void*, void*, int, int, int, int, int, int, int, int,
                           cudaStream_t);
 int fwb_shortconv(const void*, int, const float*, const float*, float*, const int*, const int*, const int*,
@@ -261,7 +261,7 @@ void tc_gemm(Launches& L, const void* x, const void* w, void* out, int out_bf16,
         stages = ring_depth(M, N, splits, 1);
         tile_tokens = decode_tile(M, N);
     }
-    L.add(fwb_gemm_tcgen05(x, w, out, addend, M, N, K, N, N, epilogue, 0, splits, stages, tile_tokens, -1, stream));
+    L.add(fwb_gemm_tcgen05(x, w, out, addend, M, N, K, N, N, epilogue, 0, splits, stages, tile_tokens, -1, 0.0f, stream));
 }
 
 // silu(x @ gate^T) * (x @ up^T) for w = [gate rows | up rows] ([2F][K]) -> out [M][F] bf16.
@@ -277,13 +277,13 @@ void tc_swiglu(Launches& L, const void* x, const void* w, void* out, int M, int 
     const int cut = (M > 128 && splits == 1 && !stages && !tile_tokens && !mid) ? wave_cut(M, F) : 0;
     if (cut) {
         const int first = cut * 128;
-        L.add(fwb_gemm_tcgen05(x, w, out, nullptr, M, first, K, 2 * F, F, EPI_SWIGLU_BF16, F, 1, 0, 256, -1, stream));
+        L.add(fwb_gemm_tcgen05(x, w, out, nullptr, M, first, K, 2 * F, F, EPI_SWIGLU_BF16, F, 1, 0, 256, -1, 0.0f, stream));
         L.add(fwb_gemm_tcgen05(x, offset(w, (long long)first * K, 2), (void*)offset(out, first, 2), nullptr, M,
-                               F - first, K, 2 * F - first, F, EPI_SWIGLU_BF16, F, 1, 0, 128, -1, stream));
+                               F - first, K, 2 * F - first, F, EPI_SWIGLU_BF16, F, 1, 0, 128, -1, 0.0f, stream));
         return;
     }
     L.add(fwb_gemm_tcgen05(x, w, out, nullptr, M, F, K, 2 * F, F, EPI_SWIGLU_BF16, F, splits, stages, tile_tokens,
-                           -1, stream));
+                           -1, 0.0f, stream));
 }
 
 // The product the model uses, from activations that are already there (kernels/ops.py: linear).
@@ -433,7 +433,7 @@ void run_norm_linear(Launches& L, const Op& op, const FwbStep& step, bool& pendi
         tile_tokens = decode_tile(M, op.N);
         L.add(fwb_gemm_tcgen05_normed(op.x, op.v0, rows, op.eps, op.w, out, M, op.N, op.K,
                                       swiglu ? 2 * op.N : op.N, op.N, op.epilogue, swiglu ? op.N : 0, splits,
-                                      stages, tile_tokens, stream));
+                                      stages, tile_tokens, 0.0f, stream));
         return;
     }
     // the norm kernel first (it also adds a pending delta into the residual), into scratch rows

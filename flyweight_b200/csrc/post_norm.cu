@@ -4,7 +4,8 @@
 //   fwb_rmsnorm_add:   x[t] += w * y[t] / sqrt(mean(y[t]^2) + eps)                 (fp32, in place)
 //                      and, when a second weight is given, the norm that the next sublayer reads,
 //                      h[t] = w2 * x[t] / sqrt(mean(x[t]^2) + eps2), from the new x in the same pass
-//   fwb_gate_act_mul:  out[t][f] = act(gu[t][f]) * gu[t][F + f],  act = silu | gelu (tanh form)
+//   fwb_gate_act_mul:  out[t][f] = act(gu[t][f]) * gu[t][F + f],  act = silu | gelu (tanh form); or the clamped
+//                      swish, min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1)
 // All arithmetic is fp32; a row is summed in an order that depends on its length alone.
 #include "common.cuh"
 
@@ -41,14 +42,15 @@ rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const flo
 }
 
 template <typename TI, typename TO>
-__global__ void gate_act_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int T, int F, int act) {
+__global__ void gate_act_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int T, int F, int act,
+                                    float limit) {
     fwb::pdl_entry();
     const size_t n = (size_t)T * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / F, f = i - t * F;
         const float g = to_f32<TI>(gu[t * 2 * F + f]);
         const float u = to_f32<TI>(gu[t * 2 * F + F + f]);
-        out[i] = from_f32<TO>((act == 1 ? gelu_tanh_f32(g) : silu_f32(g)) * u);
+        out[i] = from_f32<TO>(gated_f32(act, limit, g, u));
     }
 }
 
@@ -73,21 +75,22 @@ FWB_API int fwb_rmsnorm_add(float* x, const float* y, const float* w, float eps,
     return fwb_launch_status();
 }
 
-// gu: [T][2F] (gate columns, then up columns); out: [T][F].  act: 0 silu, 1 gelu (tanh form).
+// gu: [T][2F] (gate columns, then up columns); out: [T][F].  act: 0 silu, 1 gelu (tanh form), 2 the clamped
+// swish with its `limit`.
 FWB_API int fwb_gate_act_mul(const void* gu, int in_bf16, void* out, int out_bf16, int T, int F, int act,
-                             cudaStream_t stream) {
+                             float limit, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
-    if (!gu || !out || F <= 0 || act < 0 || act > 1) return FWB_BAD_ARGUMENT;
+    if (!gu || !out || F <= 0 || act < 0 || act > 2) return FWB_BAD_ARGUMENT;
     const size_t n = (size_t)T * F;
     const int blocks = (int)((n + 255) / 256 > 8192 ? 8192 : (n + 255) / 256);
     if (in_bf16 && out_bf16)
         fwb::pdl(gate_act_mul_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream)(
-            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F, act);
+            (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F, act, limit);
     else if (!in_bf16 && out_bf16)
         fwb::pdl(gate_act_mul_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream)(
-            (const float*)gu, (__nv_bfloat16*)out, T, F, act);
+            (const float*)gu, (__nv_bfloat16*)out, T, F, act, limit);
     else if (!in_bf16 && !out_bf16)
-        fwb::pdl(gate_act_mul_kernel<float, float>, blocks, 256, 0, stream)((const float*)gu, (float*)out, T, F, act);
+        fwb::pdl(gate_act_mul_kernel<float, float>, blocks, 256, 0, stream)((const float*)gu, (float*)out, T, F, act, limit);
     else
         return FWB_UNSUPPORTED;
     return fwb_launch_status();

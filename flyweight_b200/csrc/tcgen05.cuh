@@ -222,6 +222,17 @@ __device__ __forceinline__ float gate_act_fast(int act, float g) {
     const float z = act == GATE_GELU_TANH ? 1.5957691216057308f * fmaf(0.044715f * g, g * g, g) : g;
     return __fdividef(g, 1.0f + __expf(-z));
 }
+// The gated value of the epilogue, act(g) * u; 2 = the clamped swish (g cut off above `limit`, u held inside
+// [-limit, limit], g sigmoid(1.702 g) (u + 1)), the same quotient once more.
+constexpr int GATE_SWISH_CLAMPED = 2;
+__device__ __forceinline__ float gated_fast(int act, float limit, float g, float u) {
+    if (act == GATE_SWISH_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+        return __fdividef(g, 1.0f + __expf(-1.702f * g)) * u;
+    }
+    return gate_act_fast(act, g) * u;
+}
 
 // K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {

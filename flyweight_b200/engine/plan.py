@@ -549,6 +549,8 @@ def build_plan(model, caches, max_tokens: int, max_rows: int, num_slots: int, n_
             own = len(spec.schedule)
             embedder.plan(builder, model.embedding, spec.vocab_size, caches[own] if len(caches) > own else None)
         for position, entry in enumerate(spec.schedule):
+            if entry.add_embedding:
+                raise NotPlannable("a schedule that adds the embedding's output again has no native form")
             source = position if entry.cache_of is None else entry.cache_of
             layer = model.layers[entry.layer]
             plan = getattr(layer, "plan", None)

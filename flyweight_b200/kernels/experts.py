@@ -35,8 +35,23 @@ def route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, n_gro
     return ids, weights
 
 
+def route_table(token_ids: torch.Tensor, table: torch.Tensor, top: int):
+    """ids int32 [T][top] and weights fp32 [T][top] of a router that is a table: row ``token_ids[t]`` of
+    ``table`` (int32 [vocab][top]) names the token's experts, each with weight 1 / top."""
+    check_tensor("token ids", token_ids, torch.int32)
+    check_tensor("expert table", table, torch.int32)
+    if table.dim() != 2 or table.shape[1] != top:
+        raise KernelError(f"the expert table must be [vocab][{top}], got {tuple(table.shape)}")
+    T = token_ids.numel()
+    ids = torch.empty((T, top), dtype=torch.int32, device=table.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=table.device)
+    lib.call("fwb_moe_route_table", ptr(token_ids), ptr(table), table.shape[0], int(top), T, ptr(ids), ptr(weights),
+             stream())
+    return ids, weights
+
+
 def experts_forward(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-                    w_down: torch.Tensor, activation: str = "silu", add_normed_into=None):
+                    w_down: torch.Tensor, activation: str = "silu", add_normed_into=None, limit: float = 0.0):
     """``sum_slot weights * expert(h)`` as fp32 [T][W].  ``w_gate_up``: [E][2F][W] (gate rows, then up
     rows), ``w_down``: [E][W][F], both in the dtype of ``h``.  Router outputs from E on are identity
     experts: they pass ``h`` itself on.  ``add_normed_into`` = (x, norm weight, eps): the sum is not
@@ -75,15 +90,15 @@ def experts_forward(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
         rows = torch.empty((A, W), dtype=h.dtype, device=dev)
         lib.call("fwb_moe_gather_rows", ptr(h), ptr(row_token), ptr(offsets), E, ptr(rows), A, W, stream())
         lib.call("fwb_gemm_tcgen05_grouped", ptr(rows), ptr(w_gate_up), ptr(a), ptr(offsets), ptr(tiles), max_tiles,
-                 tile_rows, A, F, W, E, 2 * F, F, _gated_epilogue(activation), F, stream(),
+                 tile_rows, A, F, W, E, 2 * F, F, _gated_epilogue(activation), F, c_float(limit), stream(),
                  tag=f"experts gate|up {F}x{W}")
         lib.call("fwb_gemm_tcgen05_grouped", ptr(a), ptr(w_down), ptr(y), ptr(offsets), ptr(tiles), max_tiles,
-                 tile_rows, A, W, F, E, W, W, EPI_F32, 0, stream(), tag=f"experts down {W}x{F}")
+                 tile_rows, A, W, F, E, W, W, EPI_F32, 0, c_float(0.0), stream(), tag=f"experts down {W}x{F}")
     elif E > 0:                                 # (a router may have identity experts only)
         lib.call("fwb_moe_gemm", ptr(h), ptr(w_gate_up), bf16, ptr(a), ptr(offsets), ptr(row_token), ptr(tiles),
-                 max_tiles, F, W, 1, act, stream())
+                 max_tiles, F, W, 1, act, c_float(limit), stream())
         lib.call("fwb_moe_gemm", ptr(a), ptr(w_down), bf16, ptr(y), ptr(offsets), ptr(row_token), ptr(tiles),
-                 max_tiles, W, F, 0, 0, stream())
+                 max_tiles, W, F, 0, 0, c_float(0.0), stream())
     if add_normed_into is not None:
         x, norm_weight, eps = add_normed_into
         check_tensor("residual", x, torch.float32, (T, W))

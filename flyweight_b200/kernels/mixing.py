@@ -42,6 +42,28 @@ def rmsnorm_ranges_(buf: torch.Tensor, ranges) -> torch.Tensor:
     return buf
 
 
+def causal_conv(rows: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tensor], batch) -> torch.Tensor:
+    """A causal convolution over time on every channel of ``rows`` ([T][C], fp32 or bf16), ``taps`` fp32 [C][n]
+    with the last tap on the token itself: ``y[t] = sum_j taps[:, j] * rows[t - n + 1 + j]`` along each
+    request's tokens.  ``state``: fp32 [slots][n - 1][C], every live request's last n - 1 inputs (zero when it
+    starts), read in front of a portion and moved on by this call (None when n == 1).  Returns a new buffer."""
+    check_tensor("convolution input", rows)
+    T, C = rows.shape
+    n = taps.shape[1]
+    check_tensor("convolution taps", taps, torch.float32, (C, n))
+    stride = 0
+    if n > 1:
+        if state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (n - 1, C) \
+                or state.stride(2) != 1 or state.stride(1) != C:
+            raise KernelError(f"the convolution's state must be fp32 [slots][{n - 1}][{C}] with contiguous slots")
+        stride = state.stride(0) if state.shape[0] > 1 else (n - 1) * C
+    out = torch.empty_like(rows)
+    lib.call("fwb_causal_conv", ptr(rows), ptr(out), is_bf16(rows), c_longlong(C), 0, C, ptr(taps), n,
+             ptr(state) if n > 1 else None, c_longlong(stride), ptr(batch.tok_seg), ptr(batch.seg_start),
+             ptr(batch.seg_slot), T, batch.n_segments, stream(), launches=2 if n > 1 else 1)
+    return out
+
+
 def value_mix_(rows: torch.Tensor, col0: int, width: int, first: torch.Tensor,
                lam: Optional[torch.Tensor]) -> None:
     """``lam`` None: ``first[t][:] = rows[t][col0 : col0 + width]`` (the values a later layer mixes in).

@@ -191,12 +191,15 @@ def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
-GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+# what a gated feed-forward makes of gate g and up u: silu(g) u, gelu(g) u (tanh form), or the clamped swish
+# min(g, L) sigmoid(1.702 min(g, L)) (clamp(u, -L, L) + 1) with a limit L
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
 
 
-def gate_act_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, activation: str = "silu") -> torch.Tensor:
-    """``act(gate) * up`` for ``gate_up`` = [T][gate(F) | up(F)]; ``activation``: "silu" or "gelu_tanh"
-    (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))))."""
+def gate_act_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, activation: str = "silu",
+                 limit: float = 0.0) -> torch.Tensor:
+    """``act(gate) * up`` for ``gate_up`` = [T][gate(F) | up(F)]; ``activation``: "silu", "gelu_tanh"
+    (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))) or "swish_clamped" with its ``limit``."""
     check_tensor("gate|up", gate_up)
     T, F2 = gate_up.shape
     if F2 % 2:
@@ -206,7 +209,8 @@ def gate_act_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, activation: str 
     except KeyError:
         raise KernelError(f"unknown gate activation {activation!r}; known: " + ", ".join(GATE_ACTIVATIONS)) from None
     out = torch.empty((T, F2 // 2), dtype=out_dtype, device=gate_up.device)
-    lib.call("fwb_gate_act_mul", ptr(gate_up), is_bf16(gate_up), ptr(out), is_bf16(out), T, F2 // 2, act, stream())
+    lib.call("fwb_gate_act_mul", ptr(gate_up), is_bf16(gate_up), ptr(out), is_bf16(out), T, F2 // 2, act,
+             lib.c_float(limit), stream())
     return out
 
 

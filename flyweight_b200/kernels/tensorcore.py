@@ -231,7 +231,7 @@ def gemm(x, w, out_dtype, addend=None, splits=None, stages=0, tile_tokens=0, wid
         stages = stages or _ring_depth(M, N, splits, 1)
         tile_tokens = tile_tokens or _decode_tile(M, N)
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w), ptr(out), ptr(addend), M, N, K, N, N, epilogue, 0,
-             splits, stages, tile_tokens, wide, stream(), tag=f"{N}x{K} splits {splits}")
+             splits, stages, tile_tokens, wide, lib.c_float(0.0), stream(), tag=f"{N}x{K} splits {splits}")
     return out
 
 
@@ -239,9 +239,10 @@ def swiglu_accepts(x, w_gate_up) -> bool:
     return accepts(x, w_gate_up, torch.bfloat16)
 
 
-def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0, activation="silu") -> torch.Tensor:
+def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0, activation="silu", limit=0.0) -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` as bf16, for ``w_gate_up`` = [gate rows | up rows]:
-    both products accumulate side by side in tensor memory and never reach global memory."""
+    both products accumulate side by side in tensor memory and never reach global memory.
+    ``activation`` names another gated form (``ops.GATE_ACTIVATIONS``), ``limit`` its parameter."""
     check_tensor("swiglu input", x, torch.bfloat16)
     check_tensor("swiglu weight", w_gate_up, torch.bfloat16)
     M, K = x.shape
@@ -273,12 +274,14 @@ def swiglu_gate_up(x, w_gate_up, splits=None, stages=0, tile_tokens=0, activatio
         # as many CTAs of half the length, which fit one wave and start as the first launch drains.
         first = cut * 128
         lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, first, K, F2, F,
-                 gated, F, 1, 0, 256, -1, stream(), tag=f"swiglu {F}x{K} first")
+                 gated, F, 1, 0, 256, -1, lib.c_float(limit), stream(), tag=f"swiglu {F}x{K} first")
         lib.call("fwb_gemm_tcgen05", ptr(x), _offset(w_gate_up, first * K), _offset(out, first), ptr(None), M,
-                 F - first, K, F2 - first, F, gated, F, 1, 0, 128, -1, stream(), tag=f"swiglu {F}x{K} rest")
+                 F - first, K, F2 - first, F, gated, F, 1, 0, 128, -1, lib.c_float(limit), stream(),
+                 tag=f"swiglu {F}x{K} rest")
         return out
     lib.call("fwb_gemm_tcgen05", ptr(x), ptr(w_gate_up), ptr(out), ptr(None), M, F, K, F2, F,
-             gated, F, splits, stages, tile_tokens, -1, stream(), tag=f"swiglu {F}x{K} splits {splits}")
+             gated, F, splits, stages, tile_tokens, -1, lib.c_float(limit), stream(),
+             tag=f"swiglu {F}x{K} splits {splits}")
     return out
 
 
@@ -363,12 +366,12 @@ def gemm_normed(x_res, norm_weight, eps, w, out_dtype, rows=None, n_rows=None, s
     tile_tokens = tile_tokens or _decode_tile(M, N)
     lib.call("fwb_gemm_tcgen05_normed", ptr(x_res), ptr(norm_weight), ptr(rows), lib.c_float(eps), ptr(w),
              ptr(out), M, N, K, N, N, EPI_F32 if out_dtype == torch.float32 else EPI_BF16, 0, splits,
-             stages, tile_tokens, stream(), tag=f"normed {N}x{K} splits {splits}")
+             stages, tile_tokens, lib.c_float(0.0), stream(), tag=f"normed {N}x{K} splits {splits}")
     return out
 
 
 def swiglu_gate_up_normed(x_res, norm_weight, eps, w_gate_up, splits=None, stages=0, tile_tokens=0,
-                          activation="silu") -> torch.Tensor:
+                          activation="silu", limit=0.0) -> torch.Tensor:
     """``silu(n @ gate.T) * (n @ up.T)`` with n = rmsnorm(x_res), in one kernel."""
     check_tensor("residual", x_res, torch.float32)
     check_tensor("norm weight", norm_weight, torch.float32)
@@ -387,7 +390,7 @@ def swiglu_gate_up_normed(x_res, norm_weight, eps, w_gate_up, splits=None, stage
     tile_tokens = tile_tokens or _decode_tile(M, F)
     lib.call("fwb_gemm_tcgen05_normed", ptr(x_res), ptr(norm_weight), ptr(None), lib.c_float(eps),
              ptr(w_gate_up), ptr(out), M, F, K, F2, F, gated, F, splits, stages, tile_tokens,
-             stream(), tag=f"normed swiglu {F}x{K} splits {splits}")
+             lib.c_float(limit), stream(), tag=f"normed swiglu {F}x{K} splits {splits}")
     return out
 
 

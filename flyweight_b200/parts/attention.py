@@ -14,7 +14,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorDecl
-from .base import Mixer, PagedKV, Precision, build_position, register_mixer
+from .base import FixedState, Mixer, PagedKV, Precision, build_position, register_mixer
 
 
 @register_mixer("gqa_attention")
@@ -34,7 +34,11 @@ class GQAttention(Mixer):
     one weight of ``head_dim`` entries shared by the heads, the mean over each head; "whole": the RMS norm
     goes over all heads of q (and of k) at once, before they are split, with weights of the whole
     projection's size); ``sink`` (True: tensor ``sink`` [heads], a score per head that joins every softmax
-    denominator without a value, neither scaled nor capped); ``softcap`` (> 0: score <- cap tanh(score /
+    denominator without a value, neither scaled nor capped; "zero": that score is 0 for every head and there
+    is no tensor, i.e. the denominator is one larger); ``conv`` (n > 0: a causal convolution of n taps over
+    time on every channel of q, k and v right behind their projection, tensors ``q_conv``, ``k_conv``,
+    ``v_conv`` [channels][n], the last tap on the token itself; a request's last n - 1 projected rows are
+    kept in a ``FixedState`` beside the pages); ``softcap`` (> 0: score <- cap tanh(score /
     cap) behind the scale); ``gate`` ("head": tensor ``g`` [heads][H], every head's output times
     sigmoid(g h) of its head; "element": ``g`` [heads value_dim][H], channel by channel; both read the
     mixer's input); ``value_mix`` ("source": this layer's values, as cached, are also handed on to later
@@ -75,6 +79,8 @@ class GQAttention(Mixer):
         if self.qk_norm == "whole" and self.eps is None:
             raise ValueError("a q/k norm over the whole projection needs qk_norm_eps")
         self.has_sink = bool(p.get("sink", False))
+        self.zero_sink = p.get("sink") == "zero"
+        self.conv_taps = int(p.get("conv", 0) or 0)
         self.softcap = float(p.get("softcap", 0.0) or 0.0)
         self.gate = p.get("gate")
         if self.gate not in (None, "head", "element"):
@@ -90,13 +96,14 @@ class GQAttention(Mixer):
         if self.value_dim != self.qk_dim or self.qk_dim % 16:
             self.head_dim = -(-max(self.qk_dim, self.value_dim) // 16) * 16
         # the launches LFM2 makes: nothing of the above, so the fused decode kernel and the native plan apply
-        self._plain = not (self.has_sink or self.softcap or self.gate or self.value_mix
+        self._plain = not (self.has_sink or self.softcap or self.gate or self.value_mix or self.conv_taps
                            or self.qk_norm == "whole" or (self.head_dim != self.qk_dim and self.eps is not None))
         # q|k|v leave their product in fp32 when a norm over the whole projection works on them in place before
         # the head kernel reads them: one rounding, not two.  (Mixed values are rounded on both sides of the
         # mix in 16-bit runs: what the products' dtype means for a projection and for a cached value.)
         self._wide_qkv = self.qk_norm == "whole"
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.w_gate = self.sink = self.vmix = None
+        self.taps = None
 
     @property
     def _kv_in(self) -> int:
@@ -114,8 +121,13 @@ class GQAttention(Mixer):
             out[n["q_norm"]] = TensorDecl((self.n_heads * hd if whole else hd,), "norm")
             if not self.shares_cache:
                 out[n["k_norm"]] = TensorDecl((self.n_kv * hd if whole else hd,), "norm")
-        if self.has_sink:
+        if self.has_sink and not self.zero_sink:
             out[n["sink"]] = TensorDecl((self.n_heads,), "bias")
+        if self.conv_taps:
+            out[n["q_conv"]] = TensorDecl((self.n_heads * hd, self.conv_taps), "taps")
+            if not self.shares_cache:
+                out[n["k_conv"]] = TensorDecl((self.n_kv * hd, self.conv_taps), "taps")
+                out[n["v_conv"]] = TensorDecl((self.n_kv * self.value_dim, self.conv_taps), "taps")
         if self.gate:
             out[n["g"]] = TensorDecl((self.n_heads * (self.value_dim if self.gate == "element" else 1), H))
         if self.value_mix == "mixed":
@@ -162,7 +174,14 @@ class GQAttention(Mixer):
             if not self.shares_cache:
                 self.k_norm = precision.vector(channels_padded(get(n["k_norm"]), self.qk_dim), device)
         if self.has_sink:
-            self.sink = precision.vector(get(n["sink"]), device)
+            self.sink = (torch.zeros(self.n_heads, dtype=torch.float32, device=device) if self.zero_sink
+                         else precision.vector(get(n["sink"]), device))
+        if self.conv_taps:
+            # the taps of q | k | v in the fused projection's channel order (zero taps on padding channels)
+            taps = [rows_padded(get(n["q_conv"]), self.qk_dim)]
+            if not self.shares_cache:
+                taps += [rows_padded(get(n["k_conv"]), self.qk_dim), rows_padded(get(n["v_conv"]), self.value_dim)]
+            self.taps = precision.vector(torch.cat([t.to(torch.float32) for t in taps], dim=0), device)
         if self.gate:
             w_gate = get(n["g"])
             self.w_gate = precision.matrix(rows_padded(w_gate, self.value_dim) if self.gate == "element" else w_gate,
@@ -201,7 +220,12 @@ class GQAttention(Mixer):
         return {"unit_rms_after": True, "norm_dim": self.qk_dim}
 
     def state_spec(self):
-        return None if self.shares_cache else PagedKV(self.n_kv, self.head_dim, self.window)
+        paged = None if self.shares_cache else PagedKV(self.n_kv, self.head_dim, self.window)
+        if self.conv_taps > 1:
+            channels = (self.n_heads + 2 * self._kv_in) * self.head_dim
+            rolling = FixedState((self.conv_taps - 1, channels))
+            return rolling if paged is None else (paged, rolling)
+        return paged
 
     def prepare(self, max_positions, device):
         self.position.prepare(max_positions, device)
@@ -244,6 +268,8 @@ class GQAttention(Mixer):
         qkv = ops.linear(h, self.w_qkv, torch.float32 if self._wide_qkv else act)
         block_table = ctx.batch.block_tables[cache.group]
         k_at, v_at = self.n_heads * D, (self.n_heads + self._kv_in) * D
+        if self.conv_taps:
+            qkv = mixing.causal_conv(qkv, self.taps, cache.state if self.conv_taps > 1 else None, ctx.batch)
         whole = self.qk_norm == "whole"
         if whole:
             ranges = [(0, self.q_norm, self.n_heads * self.qk_dim, self.eps)]

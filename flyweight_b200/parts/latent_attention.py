@@ -40,8 +40,9 @@ class LatentAttention(Mixer):
     """params: hidden_size, num_heads, dim (plain query/key channels per head), rot_dim (turned
     ones), vdim, kv_rank, scale, eps (of the latent's norm), position (PartSpec of a rotary encoding
     whose ``rotary_dim`` <= rot_dim), sink (True: a learned number per head joins the softmax
-    denominator), shares_cache (True: reads the rows of another execution; no latent projection).
-    tensors: q, dkv, dkv_norm, uk, uv, o, sink."""
+    denominator), shares_cache (True: reads the rows of another execution; no latent projection), gate
+    ("head": tensor ``g`` [heads][H], every head's output times sigmoid(g h) of its head, from the mixer's
+    own input).  tensors: q, dkv, dkv_norm, uk, uv, o, sink, g."""
     graph_safe = True
 
     def __init__(self, spec):
@@ -57,6 +58,9 @@ class LatentAttention(Mixer):
         self.eps = float(p["eps"])
         self.has_sink = bool(p.get("sink", False))
         self.shares_cache = bool(p.get("shares_cache", False))
+        self.gate = p.get("gate")
+        if self.gate not in (None, "head"):
+            raise ValueError(f"unknown output gate {self.gate!r}; known: head")
         self.position = build_position(p["position"])
         if self.position.rotary_dim > self.rot:
             raise ValueError(f"{self.position.rotary_dim} turning channels but a rotated part of {self.rot}")
@@ -67,7 +71,7 @@ class LatentAttention(Mixer):
         used = self.rank + self.rot
         self.row = 64 if used <= 64 else (128 if 96 < used <= 128 else _round_up(used, 16))
         self.q_width = self.n_heads * (self.dim + self.rot)
-        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.norm_w = self.sink = None
+        self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.norm_w = self.sink = self.w_gate = None
 
     def declare(self):
         n, H = self.names, self.hidden
@@ -80,6 +84,8 @@ class LatentAttention(Mixer):
             out[n["dkv_norm"]] = TensorDecl((self.rank,), "norm")
         if self.has_sink:
             out[n["sink"]] = TensorDecl((self.n_heads,), "bias")
+        if self.gate:
+            out[n["g"]] = TensorDecl((self.n_heads, H))
         return out
 
     def bind(self, get, precision: Precision, device):
@@ -98,9 +104,11 @@ class LatentAttention(Mixer):
             self.norm_w = precision.vector(get(n["dkv_norm"]), device)
         if self.has_sink:
             self.sink = precision.vector(get(n["sink"]), device)
+        if self.gate:
+            self.w_gate = precision.matrix(get(n["g"]), device)
 
     def _matrices(self):
-        return (self.w_in, self.w_uk_t, self.w_uv, self.w_o)
+        return tuple(m for m in (self.w_in, self.w_uk_t, self.w_uv, self.w_o, self.w_gate) if m is not None)
 
     def weight_bytes(self):
         return sum(m.numel() * m.element_size() for m in self._matrices())
@@ -125,6 +133,8 @@ class LatentAttention(Mixer):
         rotation = self.position.rotation()
         if rotation is None:
             raise NotPlannable(f"position encoding {self.position.kind!r} is no plain rotation")
+        if self.gate:
+            raise NotPlannable("an output gate on the latent attention has no native plan form")
         table, rot_dims, pairing = rotation
         act = builder.act_dtype
         proj = builder.tokens(self.w_in.shape[0], act)
@@ -171,4 +181,7 @@ class LatentAttention(Mixer):
             stride = self.rank
         heads_out = torch.empty((mixed.shape[0], self.n_heads * self.vdim), dtype=act, device=mixed.device)
         latent_kernels.head_linear(mixed, 0, stride, self.rank, self.w_uv, heads_out, 0, self.vdim)
+        if self.gate:
+            from ..kernels import mixing
+            mixing.sigmoid_gate_mul_(heads_out, ops.linear(h, self.w_gate, act), self.n_heads, self.vdim)
         return ops.linear(heads_out, self.w_o, torch.float32)

@@ -133,7 +133,14 @@ class DecoderModel:
             own = len(self.spec.schedule)
             x = self.embedder.forward(ctx, self.embedding, caches[own] if len(caches) > own else None)
         pending = None
+        # a schedule that feeds the embedding's output to later executions keeps a copy of it
+        first = x.clone() if any(entry.add_embedding for entry in self.spec.schedule) else None
         for position, entry in enumerate(self.spec.schedule):
+            if entry.add_embedding:
+                if pending is not None:
+                    ops.add_(x, pending)
+                    pending = None
+                ops.add_(x, first)
             # a position that reads another's pages finds them in its own entry (the manager puts
             # them there), beside the fixed-size state that is its own
             x, pending = self.layers[entry.layer].forward(ctx, x, pending, caches[position])

@@ -104,3 +104,110 @@ class RoutedExperts(FeedForward):
         """``x += norm_weight * unit(ff(h))`` with the weighted sum, the output norm and the residual sum in
         one kernel (an arrangement with a norm on the sublayer's output asks for it)."""
         self.forward(ctx, h, add_normed_into=(x, norm_weight, eps))
+
+
+@register_feed_forward("table_experts")
+class TableExperts(FeedForward):
+    """Experts chosen by the token's id instead of a router: row ``id`` of an integer table names the
+    token's ``top`` experts (the entries of a row differ), each counts 1 / top, and the result is the sum;
+    an optional shared expert of its own width runs for every token and is added.  Every expert is a gated
+    feed-forward ``down(act(gate h, up h))`` without biases.
+
+    params: hidden_size, vocab_size, ffn_dim (of one expert), experts, top, activation ("silu", "gelu_tanh" or
+    "swish_clamped"), limit (of "swish_clamped"), and optionally shared_ffn_dim (> 0: there is a shared expert)
+    with shared_limit.  tensors: table [vocab][top] (integers), per expert j ``gate{j}``, ``up{j}`` [F][H],
+    ``down{j}`` [H][F], and ``shared_gate``, ``shared_up`` [Fs][H], ``shared_down`` [H][Fs]."""
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.vocab = int(p["vocab_size"])
+        self.ffn_dim = int(p["ffn_dim"])
+        self.n_experts = int(p["experts"])
+        self.top = int(p["top"])
+        self.activation = str(p.get("activation", "silu"))
+        self.limit = float(p.get("limit", 0.0) or 0.0)
+        self.shared_ffn = int(p.get("shared_ffn_dim", 0) or 0)
+        self.shared_limit = float(p.get("shared_limit", self.limit) or 0.0)
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"unknown gate activation {self.activation!r}")
+        if not 0 < self.top <= self.n_experts:
+            raise ValueError(f"top {self.top} of {self.n_experts} experts")
+        if self.activation == "swish_clamped" and (self.limit <= 0 or (self.shared_ffn and self.shared_limit <= 0)):
+            raise ValueError("the clamped swish needs a positive limit")
+        self.table = self.w_gate_up = self.w_down = self.shared_gate_up = self.shared_down = None
+
+    def declare(self):
+        n, H, F = self.names, self.hidden, self.ffn_dim
+        out = {n["table"]: TensorDecl((self.vocab, self.top), "table", bound=self.n_experts)}
+        for j in range(self.n_experts):
+            out[n[f"gate{j}"]] = TensorDecl((F, H))
+            out[n[f"up{j}"]] = TensorDecl((F, H))
+            out[n[f"down{j}"]] = TensorDecl((H, F))
+        if self.shared_ffn:
+            out[n["shared_gate"]] = TensorDecl((self.shared_ffn, H))
+            out[n["shared_up"]] = TensorDecl((self.shared_ffn, H))
+            out[n["shared_down"]] = TensorDecl((H, self.shared_ffn))
+        return out
+
+    def bind(self, get, precision: Precision, device):
+        n = self.names
+        table = get(n["table"]).to(torch.int32)
+        if int(table.min()) < 0 or int(table.max()) >= self.n_experts:
+            raise ValueError(f"{n['table']} names an expert outside [0, {self.n_experts})")
+        self.table = table.to(device).contiguous()
+        mats = [get(n[f"{role}{j}"]) for j in range(self.n_experts) for role in ("gate", "up", "down")]
+        dtype = torch.float32 if (precision.name == "float32" or len({m.dtype for m in mats}) > 1) else mats[0].dtype
+        # [E][gate rows | up rows][H] and [E][H][F]: one stacked tensor per product
+        self.w_gate_up = torch.stack([torch.cat([get(n[f"gate{j}"]).to(dtype), get(n[f"up{j}"]).to(dtype)], dim=0)
+                                      for j in range(self.n_experts)]).to(device).contiguous()
+        self.w_down = torch.stack([get(n[f"down{j}"]).to(dtype) for j in range(self.n_experts)]).to(device).contiguous()
+        if self.shared_ffn:
+            gate, up = get(n["shared_gate"]), get(n["shared_up"])
+            if gate.dtype != up.dtype:
+                gate, up = gate.to(torch.float32), up.to(torch.float32)
+            self.shared_gate_up = precision.matrix(torch.cat([gate, up], dim=0), device)
+            self.shared_down = precision.matrix(get(n["shared_down"]), device)
+
+    def _shared_bytes(self):
+        if not self.shared_ffn:
+            return 0
+        return (self.shared_gate_up.numel() * self.shared_gate_up.element_size()
+                + self.shared_down.numel() * self.shared_down.element_size())
+
+    def weight_bytes(self):
+        return (self.table.numel() * 4 + self._shared_bytes()
+                + self.w_gate_up.numel() * self.w_gate_up.element_size()
+                + self.w_down.numel() * self.w_down.element_size())
+
+    def active_weight_bytes(self, n_tokens):
+        chosen = min(self.n_experts, n_tokens * self.top)
+        per_expert = 3 * self.ffn_dim * self.hidden * self.w_gate_up.element_size()
+        return n_tokens * self.top * 4 + chosen * per_expert + self._shared_bytes()
+
+    def flops_per_token(self):
+        return 2.0 * 3 * self.hidden * (self.top * self.ffn_dim + self.shared_ffn)
+
+    def _shared_hidden(self, ctx, h):
+        """act(gate h, up h) of the shared expert, in the products' dtype."""
+        from ..kernels import tensorcore
+        act = ctx.precision.act_dtype
+        if tensorcore.swiglu_accepts(h, self.shared_gate_up):
+            return tensorcore.swiglu_gate_up(h, self.shared_gate_up, activation=self.activation,
+                                             limit=self.shared_limit)
+        gate_up = ops.linear(h, self.shared_gate_up, torch.float32)
+        return ops.gate_act_mul(gate_up, act, self.activation, self.shared_limit)
+
+    def forward(self, ctx, h):
+        ids, weights = expert_kernels.route_table(ctx.batch.token_ids, self.table, self.top)
+        rows = h if h.dtype == self.w_gate_up.dtype else ops.cast(h, self.w_gate_up.dtype)
+        out = expert_kernels.experts_forward(rows, ids, weights, self.w_gate_up, self.w_down, self.activation,
+                                             limit=self.limit)
+        if self.shared_ffn:
+            a = self._shared_hidden(ctx, h)
+            rest = ops.linear_into_residual(a, self.shared_down, out)      # out += down(a) where the product can
+            if rest is not None:
+                ops.add_(out, rest)
+        return out

@@ -13,7 +13,9 @@ from .base import DeferredNorm, Norm, Precision, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: size, eps.  tensors: weight [size]."""
+    """params: size, eps, and optionally ``gain``: one constant that multiplies the normed rows beside the
+    weight (a model that adds ``m * norm(y)`` into its stream names m here; it is folded into the weight
+    once, in fp32, when the weight is bound).  tensors: weight [size]."""
     graph_safe = True
 
 
@@ -21,6 +23,7 @@ class RMSNorm(Norm):
         super().__init__(spec)
         self.size = int(self.params["size"])
         self.eps = float(self.params["eps"])
+        self.gain = float(self.params.get("gain", 1.0))
         self.weight = None
 
     def declare(self):
@@ -28,6 +31,8 @@ class RMSNorm(Norm):
 
     def bind(self, get, precision: Precision, device):
         self.weight = precision.vector(get(self.names["weight"]), device)
+        if self.gain != 1.0:
+            self.weight = (self.weight * self.gain).contiguous()
 
     def weight_bytes(self):
         return self.size * 4

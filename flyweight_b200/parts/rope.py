@@ -24,7 +24,14 @@ class Rope(PositionEncoding):
     """params: theta, rotary_dim (even, <= head size), pairing ("half_split" | "interleaved"), and
     optionally ``scaling`` = {factor, low, high, original}: a frequency whose wavelength is shorter than
     original/high stays, one whose wavelength is longer than original/low is divided by ``factor``, and in
-    between, with s = (original/wavelength - low) / (high - low), it becomes (1 - s) f/factor + s f."""
+    between, with s = (original/wavelength - low) / (high - low), it becomes (1 - s) f/factor + s f.
+
+    ``scaling`` = {factor, original, fast, slow} (no ``low``/``high``) is the other common rule, a ramp over
+    the pair index: with c(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta) the index of the pair that
+    turns t times over ``original`` positions, lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)),
+    rotary_dim - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i gets r_i f_i / factor +
+    (1 - r_i) f_i, and every cos and sin of the table is multiplied by ``amplitude`` (0.1 ln(factor) + 1
+    when the scaling does not name one)."""
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -36,7 +43,16 @@ class Rope(PositionEncoding):
         if self.pairing not in ("half_split", "interleaved"):
             raise ValueError(f"unknown rotary pairing {self.pairing!r}")
         self.scaling = dict(self.params["scaling"]) if self.params.get("scaling") else None
-        if self.scaling is not None:
+        self.ramp = self.scaling is not None and "fast" in self.scaling
+        if self.ramp:
+            missing = [key for key in ("factor", "original", "fast", "slow") if self.scaling.get(key) is None]
+            if missing:
+                raise ValueError("rotary frequency scaling is missing " + ", ".join(missing))
+            if min(float(self.scaling[key]) for key in ("factor", "original", "fast", "slow")) <= 0 \
+                    or self.theta <= 1.0:
+                raise ValueError("rotary frequency scaling by a ramp needs positive factor, original, fast and "
+                                 "slow, and theta > 1")
+        elif self.scaling is not None:
             missing = [key for key in ("factor", "low", "high", "original") if self.scaling.get(key) is None]
             if missing:
                 raise ValueError("rotary frequency scaling is missing " + ", ".join(missing))
@@ -50,6 +66,16 @@ class Rope(PositionEncoding):
         freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), exponent)
         if self.scaling is None:
             return freq
+        if self.ramp:
+            factor, original = float(self.scaling["factor"]), float(self.scaling["original"])
+
+            def turn_index(turns: float) -> float:
+                return self.rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(turn_index(float(self.scaling["fast"]))), 0)
+            hi = min(math.ceil(turn_index(float(self.scaling["slow"]))), self.rotary_dim - 1)
+            ramp = torch.clamp((torch.arange(half, dtype=torch.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            return freq / factor * ramp + freq * (1.0 - ramp)
         factor, low, high = (float(self.scaling[key]) for key in ("factor", "low", "high"))
         original = float(self.scaling["original"])
         wave = 2.0 * math.pi / freq
@@ -57,11 +83,18 @@ class Rope(PositionEncoding):
         mixed = (1.0 - blend) * freq / factor + blend * freq
         return torch.where(wave < original / high, freq, torch.where(wave > original / low, freq / factor, mixed))
 
+    def amplitude(self) -> float:
+        """What every cos and sin is multiplied by (1 unless the scaling is a ramp)."""
+        if not self.ramp:
+            return 1.0
+        given = self.scaling.get("amplitude")
+        return float(given) if given is not None else 0.1 * math.log(float(self.scaling["factor"])) + 1.0
+
     def table(self, n_positions: int, device):
-        """[n_positions][rotary_dim/2][2] fp32: (cos, sin) of every angle."""
+        """[n_positions][rotary_dim/2][2] fp32: (cos, sin) of every angle, times ``amplitude()``."""
         inv_freq = self.frequencies()
         angle = torch.arange(n_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
-        table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).to(torch.float32)
+        table = (torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1) * self.amplitude()).to(torch.float32)
         return table.contiguous().to(device)
 
 

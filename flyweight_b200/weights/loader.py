@@ -50,10 +50,12 @@ class TensorDecl:
     """A tensor a part needs.  ``role`` picks the random initialisation
     (matrix / embedding / norm / taps / bias / table); ``also`` lists other stored
     shapes with the same bytes that are accepted and reshaped (a Conv1d weight
-    stored as [H][1][L] for a declared [H][L])."""
+    stored as [H][1][L] for a declared [H][L]).  ``bound`` (for the role "table", 0: none): the entries
+    are indices below it and the entries of a row differ; random tables are drawn so."""
     shape: Tuple[int, ...]
     role: str = "matrix"
     also: Tuple[Tuple[int, ...], ...] = ()
+    bound: int = 0
 
 
 _FLOATS = (torch.float32, torch.bfloat16, torch.float16, torch.float64)

@@ -46,6 +46,10 @@ def random_tensor(name: str, decl: TensorDecl, seed: int, preset: str = "baselin
     if decl.role == "norm":
         value = 1.0 + 0.1 * normal
     elif decl.role == "table":
+        if decl.bound > 0 and len(shape) == 2 and shape[1] <= decl.bound:
+            # every row: shape[1] different indices below the bound, in random order
+            order = torch.rand((shape[0], decl.bound), generator=gen, device=device).argsort(dim=1)
+            return order[:, :shape[1]].to(torch.int32).contiguous()
         return torch.zeros(shape, dtype=torch.int32, device=device)
     elif preset == "baseline":
         value = 0.02 * normal
