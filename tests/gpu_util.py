@@ -10,6 +10,7 @@ import numpy as np
 import torch
 
 import plain_diforax
+import plain_fobatar
 import plain_gukosun
 import plain_kemitar
 import plain_lfm2
@@ -20,7 +21,8 @@ P = plain_lfm2
 
 def plain_module(name: str):
     """The plain implementation of the tiny configuration's architecture."""
-    return {"Kemitar": plain_kemitar, "Diforax": plain_diforax, "Gukosun": plain_gukosun}.get(TINY[name].get("architecture"), plain_lfm2)
+    return {"Kemitar": plain_kemitar, "Diforax": plain_diforax, "Gukosun": plain_gukosun,
+            "Fobatar": plain_fobatar}.get(TINY[name].get("architecture"), plain_lfm2)
 
 DTYPES = ("float32", "bfloat16")
 STORED = {"float32": torch.float32, "bfloat16": torch.bfloat16}

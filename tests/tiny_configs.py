@@ -293,5 +293,106 @@ GUKOSUN_E = {
 TINY.update({"GA": GUKOSUN_A, "GB": GUKOSUN_B, "GC": GUKOSUN_C, "GD": GUKOSUN_D, "GE": GUKOSUN_E})
 
 
+def _ramp(factor, original, fast, slow):
+    return {"factor": factor, "original": original, "fast": fast, "slow": slow}
+
+
+def _conv_attention(heads, kv_heads, dim, vdim, scale, conv=None, chunk=None, rot=None):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if conv is not None:
+        mixer["conv"] = conv
+    if chunk is not None:
+        mixer["mask"] = {"size": chunk}
+    if rot is not None:
+        mixer["rot"] = rot
+    return {"type": "attention", "mixer": mixer}
+
+
+def _gated_latent(heads, dim, rot_dim, vdim, kv_rank, scale, base, scaling=None):
+    rot = {"base": base, "dims": rot_dim}
+    if scaling is not None:
+        rot["scaling"] = scaling
+    return {"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim,
+                                                  "kv_rank": kv_rank, "rot": rot, "scale": scale}}
+
+
+def _table_experts(ff, limit, experts, top, shared=None):
+    mlp = {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+    if shared is not None:
+        mlp["shared"] = {"ff": shared[0], "limit": shared[1]}
+    return mlp
+
+
+# Tiny Fobatar configurations that differ in every size and option: which layers repeat (the first two, one
+# in the middle four times, the last two, none, all of them once), both orders of the two mixers and models of
+# one mixer only, 1 to 4 query heads per key head, key and value sizes that differ both ways and sizes that are
+# no multiple of 16, 1 to 4 taps, chunks shorter than, equal to and longer than a page and a chunk of one,
+# attention without chunks, partial, full and no rotation with and without the ramp (whose three bands all
+# occur), latent rows of 32 to 128 entries, one to all experts per token, with and without the shared expert,
+# layers without a feed-forward, limits below and above 1, and the constants on the embedding and on the
+# residual sums present, absent and equal to 1.
+FOBATAR_A = {
+    "architecture": "Fobatar", "vocab": 211, "width": 80, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.5},
+    "residual_mult": 0.7, "loop": {"start": 0, "stop": 2, "times": 2},
+    "layers": [
+        {**_conv_attention(4, 2, 16, 24, 0.3, conv=4, chunk=37, rot={"base": 10000.0, "dims": 8, "scaling": _ramp(4.0, 64, 8.0, 1.0)}),
+         "mlp": _table_experts(48, 1.5, 5, 2, shared=(40, 2.5))},
+        {**_gated_latent(3, 8, 8, 20, 24, 0.25, 500.0, _ramp(2.0, 32, 4.0, 0.5)), "mlp": _table_experts(32, 3.0, 3, 1)},
+        {**_conv_attention(2, 1, 24, 24, 0.2, conv=2, chunk=64), "mlp": None},
+        {**_gated_latent(2, 16, 4, 8, 40, 0.2, 100.0), "mlp": _table_experts(16, 0.75, 4, 4, shared=(8, 1.0))},
+    ],
+}
+
+FOBATAR_B = {
+    "architecture": "Fobatar", "vocab": 130, "width": 96, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+    "residual_mult": 1.0, "loop": {"start": 2, "stop": 3, "times": 4},
+    "layers": [
+        {**_gated_latent(4, 12, 6, 12, 20, 0.3, 10000.0, _ramp(8.0, 16, 2.0, 0.25)), "mlp": _table_experts(24, 2.0, 2, 2)},
+        {**_gated_latent(1, 32, 16, 48, 64, 0.15, 1000000.0), "mlp": None},
+        {**_conv_attention(3, 3, 20, 12, 0.22, conv=3, chunk=5, rot={"base": 300.0, "dims": 20}),
+         "mlp": _table_experts(40, 0.5, 7, 3, shared=(56, 4.0))},
+        {**_conv_attention(6, 2, 8, 16, 0.35, conv=1, rot={"base": 50.0, "dims": 4, "scaling": _ramp(3.0, 8, 1.5, 0.5)}),
+         "mlp": _table_experts(24, 2.0, 2, 1, shared=(24, 2.0))},
+    ],
+}
+
+# Sizes that the tensor-core kernels take, so that the bfloat16 path runs them: heads of 64 and 128 channels,
+# four query heads per key head, latent rows of 64 and of 128 entries, expert widths in multiples of 8.
+FOBATAR_C = {
+    "architecture": "Fobatar", "vocab": 300, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.5},
+    "residual_mult": 0.25, "loop": {"start": 1, "stop": 4, "times": 2},
+    "layers": [
+        {**_conv_attention(8, 2, 64, 64, 0.12, conv=2, chunk=130, rot={"base": 1000000.0, "dims": 32, "scaling": _ramp(16.0, 256, 16.0, 2.0)}),
+         "mlp": _table_experts(64, 1.0, 6, 2, shared=(96, 3.0))},
+        {**_gated_latent(8, 32, 16, 32, 48, 0.125, 10000.0, _ramp(4.0, 64, 8.0, 1.0)), "mlp": _table_experts(32, 2.5, 4, 3)},
+        {**_conv_attention(4, 1, 128, 128, 0.09, conv=4, chunk=70, rot={"base": 10000.0, "dims": 128}),
+         "mlp": _table_experts(64, 1.0, 6, 2, shared=(96, 3.0))},
+        {**_gated_latent(4, 64, 32, 64, 96, 0.1, 20000.0), "mlp": _table_experts(128, 6.0, 3, 2, shared=(64, 0.5))},
+    ],
+}
+
+# One mixer only: latent layers alone (no state slots are needed; the constants are absent), and attention layers
+# alone (a chunk of one token, a layer without chunks, every layer once through a loop of one pass).
+FOBATAR_D = {
+    "architecture": "Fobatar", "vocab": 97, "width": 48, "norm": {"eps": 1e-6},
+    "layers": [
+        {**_gated_latent(2, 16, 8, 16, 24, 0.25, 100.0, _ramp(2.0, 16, 2.0, 1.0)), "mlp": _table_experts(80, 1.25, 3, 2, shared=(16, 1.25))},
+        {**_gated_latent(3, 8, 2, 8, 12, 0.35, 10000.0), "mlp": None},
+    ],
+}
+FOBATAR_E = {
+    "architecture": "Fobatar", "vocab": 160, "width": 64, "norm": {"eps": 1e-5}, "embedding": {"scale": 4.0},
+    "residual_mult": 1.5, "loop": {"start": 0, "stop": 3, "times": 1},
+    "layers": [
+        {**_conv_attention(4, 2, 16, 32, 0.3, conv=2, chunk=1), "mlp": _table_experts(96, 2.0, 8, 1)},
+        {**_conv_attention(2, 2, 32, 16, 0.2, conv=3, chunk=33, rot={"base": 1000.0, "dims": 32, "scaling": _ramp(2.0, 48, 6.0, 0.5)}),
+         "mlp": _table_experts(64, 1.0, 2, 2, shared=(32, 2.0))},
+        {**_conv_attention(2, 2, 32, 16, 0.2, rot={"base": 1000.0, "dims": 16}), "mlp": _table_experts(64, 1.0, 2, 2, shared=(32, 2.0))},
+    ],
+}
+
+TINY.update({"FA": FOBATAR_A, "FB": FOBATAR_B, "FC": FOBATAR_C, "FD": FOBATAR_D, "FE": FOBATAR_E})
+
+
 def vocab_of(config: dict) -> int:
     return int(config.get("vocab_size", config.get("vocab")))
