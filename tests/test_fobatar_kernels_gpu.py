@@ -227,23 +227,26 @@ def run_part(part_spec, w, dtype, h_seqs, cuts, n_pages=24, seed=0):
     return {s: torch.cat(parts) for s, parts in outs.items() if parts}
 
 
-def inputs_with_partners(lengths, width, pairs, seed, dtype, strength=6.0):
+def inputs_with_partners(lengths, width, pairs, seed, dtype, strength=6.0, query_sign=1.0):
     """Random rows; for every (sequence, key position, query position) in ``pairs`` both rows get a large
-    share of one common direction, so that this query's score on this key stands far out."""
+    share of one common direction (the query's with ``query_sign``), so that this query's score on this key
+    stands far out."""
     g = torch.Generator().manual_seed(seed)
     seqs = [torch.randn(n, width, generator=g, dtype=F64) for n in lengths]
     for index, (s, j, i) in enumerate(pairs):
         u = torch.randn(width, generator=torch.Generator().manual_seed(1000 + index), dtype=F64)
         seqs[s][j] += strength * u
-        seqs[s][i] += strength * u
+        seqs[s][i] += query_sign * strength * u
     return [bf16_round(h) if dtype == torch.bfloat16 else h.float().to(F64) for h in seqs]
 
 
 def tie_queries_to_keys(w, prefix, heads, kv, dim):
-    """Makes every query head's projection, taps and norm weight its key head's: a row that resembles an
-    earlier one then scores high on it, whatever the random weights are."""
+    """Makes every query head's projection minus its key head's, and its taps and norm weight the key head's: a
+    row that is the opposite of an earlier one then scores high on it, whatever the random weights are, and
+    every row scores far below zero on itself (else a row's own key, which no rotation turns against it,
+    would outweigh every partner)."""
     rep = heads // kv
-    w[prefix + "q"] = w[prefix + "k"].view(kv, dim, -1).repeat_interleave(rep, dim=0).reshape(heads * dim, -1).clone()
+    w[prefix + "q"] = -w[prefix + "k"].view(kv, dim, -1).repeat_interleave(rep, dim=0).reshape(heads * dim, -1).clone()
     w[prefix + "q.norm"] = w[prefix + "k.norm"].view(kv, dim).repeat_interleave(rep, dim=0).reshape(-1).clone()
     if prefix + "k.conv" in w:
         taps = w[prefix + "k.conv"]
@@ -266,31 +269,45 @@ def test_attention_inside_chunks_with_convolutions_zero_sink_and_gate(dtype, chu
     the query's chunk and at the last place of the chunk before, for queries inside a portion and for tokens
     decoded alone; the plain result with the chunk one longer or shorter, or without the sink, must differ by
     far more than the tolerance, else the inputs would prove nothing."""
-    raw = tiny_config(chunk=chunk, heads=heads, kv=kv, dim=dim, vdim=vdim, conv=conv, rot_dims=rot_dims, scale=1.2,
+    # (a scale that keeps a row's score on its partner near 10 whatever the head size: sharper rows would only
+    # magnify the 16-bit rounding of queries and keys)
+    raw = tiny_config(chunk=chunk, heads=heads, kv=kv, dim=dim, vdim=vdim, conv=conv, rot_dims=rot_dims, scale=10.0 / dim,
                       width=48 if dim < 64 else 128)
     spec, w = random_weights(raw, 3, dtype)
     tie_queries_to_keys(w, "l0.mix.", heads, kv, dim)
-    pairs = []
+    w["l0.mix.g"] = rounding(dtype)(0.25 * w["l0.mix.g"])      # (so that no gate shuts a partner's head)
+    # (sequence, query, inside?, decoded alone?): the partner is the first key of the query's chunk, or the last of
+    # the chunk before; every partner row serves one query only
+    pairs, kinds = [], {}
     if chunk > 1:
-        for i, inside in ((90, True), (102, True), (150, False), (141, False)):
+        for s, i, inside, alone in ((0, 102, True, True), (0, 150, False, False), (2, 110, True, False), (2, 64, False, True)):
             first = i - i % chunk
             j = first if inside else first - 1
             if 0 <= j < i:
-                pairs.append((0, j, i))
-    seqs = inputs_with_partners(LENGTHS, raw["width"], pairs, 7, dtype)
+                pairs.append((s, j, i))
+                kinds[(s, i)] = alone
+    seqs = inputs_with_partners(LENGTHS, raw["width"], pairs, 7, dtype, query_sign=-1.0)
     rnd = rounding(dtype)
     m = raw["layers"][0]["mixer"]
     got = run_part(spec.layers[0].parts["mixer"], w, dtype, seqs, CUTS)
+    shown, flipped = set(), set()
     for s, h in enumerate(seqs):
         pos = torch.arange(h.shape[0])
         want = P.chunked_attention_mixer(h, w, "l0.mix.", m, EPS, pos, rnd=rnd)
         close(got[s], want, TOL[dtype], f"sequence {s}")
-        if s == 0 and chunk > 1:
-            for delta in (-1, 1):
-                other = dict(m, mask={"size": chunk + delta})
-                off = P.chunked_attention_mixer(h, w, "l0.mix.", other, EPS, pos, rnd=rnd)
-                rows = [i for _, j, i in pairs if (j // chunk == i // chunk) != (j // (chunk + delta) == i // (chunk + delta))]
-                assert rows and all((off[i] - want[i]).abs().max() > SHOWS * max(1.0, want.abs().max()) for i in rows)
+        for delta in (-1, 1) if chunk > 1 else ():
+            other = dict(m, mask={"size": chunk + delta})
+            off = P.chunked_attention_mixer(h, w, "l0.mix.", other, EPS, pos, rnd=rnd)
+            for q, j, i in pairs:
+                flips = (j // chunk == i // chunk) != (j // (chunk + delta) == i // (chunk + delta))
+                if q == s and flips:
+                    flipped.add((s, i, delta))
+                    if (off[i] - want[i]).abs().max() > SHOWS * max(1.0, want.abs().max()):
+                        shown.add((s, i, delta))
+    if chunk > 1:
+        assert flipped and shown == flipped, "an edge that is one off must show wherever it changes what a query sees"
+        if chunk < 100:
+            assert {kinds[(s, i)] for s, i, _ in shown} == {True, False}     # in a portion, and decoded alone
     # the sink: a query at its chunk's first place would otherwise weigh its only key by one
     h, pos = seqs[1], torch.arange(LENGTHS[1])
     q_like = P.chunked_attention_mixer(h, w, "l0.mix.", m, EPS, pos, rnd=rnd)
