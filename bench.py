@@ -115,6 +115,32 @@ def gukosun_like(lfm2: dict, ff: int) -> dict:
             "logit_scale": 0.5, "token_side": {"dim": 64}, "layers": layers}
 
 
+def fobatar_like(lfm2: dict, ff: int) -> dict:
+    """A Fobatar configuration with the layer sizes of an LFM2 one (width, vocabulary, query and key/value
+    heads of 64; as many layer executions as LFM2 has layers: two layers fewer, with layers 2 and 3 run twice):
+    where LFM2 attends, attention over a cached latent (64 plain and 32 turned query channels a head, a latent of
+    96, so a cache row of 128); everywhere else attention inside chunks of 1,024 positions with 3-tap
+    convolutions on q, k and v.  Every layer has experts chosen by the token's id that use as much of the
+    feed-forward per token as LFM2's (16 experts of ff / 8, four a token, beside a shared expert of ff / 2)."""
+    width, heads, kv = lfm2["hidden_size"], lfm2["num_attention_heads"], lfm2["num_key_value_heads"]
+    ramp = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    mlp = {"kind": "moe", "expert": {"ff": ff // 8, "limit": 7.0}, "router": {"experts": 16, "top": 4},
+           "shared": {"ff": ff // 2, "limit": 7.0}}
+    layers = []
+    for index in range(lfm2["num_hidden_layers"] - 2):
+        if index in lfm2["full_attn_idxs"]:
+            mixer = {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 96, "scale": 0.1,
+                     "rot": {"base": 10000.0, "dims": 32, "scaling": ramp}}
+            layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+        else:
+            mixer = {"heads": heads, "kv_heads": kv, "dim": 64, "vdim": 64, "scale": 0.125, "conv": 3,
+                     "mask": {"size": 1024}, "rot": {"base": 1000000.0, "dims": 64, "scaling": ramp}}
+            layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Fobatar", "vocab": lfm2["vocab_size"], "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.5, "loop": {"start": 2, "stop": 4, "times": 2},
+            "layers": layers}
+
+
 # Kemitar, Diforax and Gukosun beside LFM2 at equal layer sizes (--compare): the feed-forward widths are what
 # LFM2's rule makes of ``intermediate_size`` at these sizes.
 KEMITAR = {"kemitar-350m": ("lfm2-350m", 4608), "kemitar-1.2b": ("lfm2-1.2b", 8192)}
@@ -126,7 +152,12 @@ for _name, (_twin, _ff) in DIFORAX.items():
 GUKOSUN = {"gukosun-350m": ("lfm2-350m", 4608), "gukosun-1.2b": ("lfm2-1.2b", 8192)}
 for _name, (_twin, _ff) in GUKOSUN.items():
     MODELS[_name] = gukosun_like(MODELS[_twin], _ff)
-COMPARE = {**KEMITAR, **DIFORAX, **GUKOSUN}
+# Fobatar beside Diforax, the closest model the engine has (a norm on both sides of every sublayer, attention
+# inside chunks, experts), at equal layer sizes
+FOBATAR = {"fobatar-350m": ("diforax-350m", 4608), "fobatar-1.2b": ("diforax-1.2b", 8192)}
+for _name, (_twin, _ff) in FOBATAR.items():
+    MODELS[_name] = fobatar_like(MODELS["lfm2" + _name[len("fobatar"):]], _ff)
+COMPARE = {**KEMITAR, **DIFORAX, **GUKOSUN, **FOBATAR}
 
 
 def vocab_of(config: dict) -> int:
@@ -255,9 +286,10 @@ def cache_bytes_read(model, context: int) -> int:
     """Bytes of cached keys and values one decoded token at ``context`` reads: per layer the positions
     its mask lets it see (a sliding window cuts them; a chunked mask through ``context_seen``)."""
     total = 0
-    seen = min(context, context_seen(model, context))
     for entry in model.spec.schedule:
         spec = model.layers[entry.layer].state_spec() if entry.cache_of is None else None
+        chunk = getattr(getattr(model.layers[entry.layer], "mixer", None), "chunk", 0)
+        seen = min(context, (context % chunk + 1 if context % chunk else chunk) if chunk else context)
         for member in (spec if isinstance(spec, tuple) else (spec,)):
             if member is not None and hasattr(member, "n_kv_heads"):
                 pools = 2 if getattr(member, "values", True) else 1
@@ -519,8 +551,8 @@ def run_sizes(args) -> int:
 
 
 def run_compare(args) -> int:
-    """``--compare kemitar-350m|kemitar-1.2b|diforax-350m|diforax-1.2b|gukosun-350m|gukosun-1.2b``: the model with random weights beside LFM2 at equal layer
-    sizes, both through the same step function -- prompts of 512, 2,048 and 8,192 tokens in one step
+    """``--compare kemitar-350m|kemitar-1.2b|diforax-350m|diforax-1.2b|gukosun-350m|gukosun-1.2b|fobatar-350m|fobatar-1.2b``: the model with
+    random weights beside its twin (LFM2; for Fobatar, Diforax) at equal layer sizes, both through the same step function -- prompts of 512, 2,048 and 8,192 tokens in one step
     (tokens/s and TFLOP/s of the model's own flop count) and decode steps at batch 1, 8 and 64 over 4,096
     cached tokens (tokens/s, and the bytes a step must read against the measured copy bandwidth).  One
     JSON line per model; the LFM2 line's ffn width is checked to be the one the Kemitar twin was given."""
@@ -534,7 +566,7 @@ def run_compare(args) -> int:
     for name in (args.compare, twin):
         config = dict(MODELS[name])
         model = Model.random(config, seed=0, dtype="bfloat16", device="cuda:0").module
-        if name == twin and model.config.ffn_dim != ff:
+        if name == twin and hasattr(model.config, "ffn_dim") and model.config.ffn_dim != ff:
             print(json.dumps({"error": f"{twin} has a feed-forward of {model.config.ffn_dim}, {args.compare} of {ff}"}))
             return 1
         vocab = vocab_of(config)
@@ -848,7 +880,8 @@ def main() -> int:
                         help="64 requests, prompts of 128 to 8,192 tokens in portions of 512 beside decoding "
                              "requests, 256 new tokens each, through the public runtime (e.g. lfm2-350m)")
     parser.add_argument("--compare", default=None, metavar="MODEL",
-                        help="kemitar-350m, kemitar-1.2b, diforax-350m, diforax-1.2b, gukosun-350m or gukosun-1.2b beside LFM2 at equal layer sizes: prompts and decode steps")
+                        help="kemitar-350m, kemitar-1.2b, diforax-350m, diforax-1.2b, gukosun-350m or gukosun-1.2b beside LFM2, "
+                             "fobatar-350m or fobatar-1.2b beside Diforax, at equal layer sizes: prompts and decode steps")
     parser.add_argument("--kernel-times", default=None, metavar="[MODEL:]decode[@BATCHxCONTEXT]|prefill|TOKENS",
                         help="one step with CUDA events around every launch: time per kernel as JSON")
     args = parser.parse_args()
