@@ -7,11 +7,15 @@
 // one request); the n - 1 inputs in front of a segment come from the request's state slot, which holds
 // the last n - 1 inputs of the sequence so far (oldest first, zero when the request starts).
 //
-//   fwb_causal_conv:  out <- conv(in) for the columns [col0, col0 + C) of every row (other columns are
-//                     not touched; `in` and `out` are different buffers of one shape), then the state of
-//                     every segment's slot moves on to the segment's last n - 1 inputs.
+//   fwb_causal_conv:  out[t][0 .. C) <- conv of the columns [col0, col0 + C) of `in` (rows `ld` entries apart;
+//                     `out` is another buffer whose rows are `out_ld` apart), then the state of every
+//                     segment's slot moves on to the segment's last n - 1 inputs.  With norm ranges (one or
+//                     two column ranges of the output, each with a weight): every range of a row is brought to
+//                     unit root mean square over `count` of its channels and multiplied by its weight before
+//                     it is written, in the same launch (a block per token keeps the row in shared memory).
 // Two launches: the convolution reads the old state, the second kernel writes the new one.  All
-// arithmetic is fp32, taps applied in the order j = 0 .. n - 1 whatever the step's cut.
+// arithmetic is fp32, taps applied in the order j = 0 .. n - 1 whatever the step's cut, and a row's sums of
+// squares are added in an order the block size alone fixes.
 #include "common.cuh"
 
 using namespace fwb;
@@ -20,9 +24,61 @@ namespace {
 
 constexpr int MAX_TAPS = 16;
 
+struct ConvNormRange {
+    int col0, width, count;
+    const float* weight;
+};
+
+// One output: the taps in the order j = 0 .. n - 1 over the token's own row and the rows before it, which lie
+// in this step's buffer (`local` tokens of the segment precede the token) or in the request's slot.
+template <typename T>
+__device__ __forceinline__ float conv_one(const T* __restrict__ in, size_t at, long long ld, const float* __restrict__ taps,
+                                          int n, int c, int C, int local, const float* __restrict__ slot) {
+    float acc = 0.0f;
+    for (int j = 0; j < n; ++j) {
+        const int back = n - 1 - j;                        // how far behind the token this tap reads
+        const float u = back <= local ? to_f32<T>(in[at - (size_t)back * ld])
+                                      : slot[(size_t)(n - 1 + local - back) * C + c];
+        acc = fmaf(taps[(size_t)c * n + j], u, acc);
+    }
+    return acc;
+}
+
+// One block per token: the convolved row stays in shared memory while the sums of squares of its one or two
+// norm ranges are reduced, then every entry leaves scaled (entries outside the ranges leave as they are).
 template <typename T>
 __global__ void __launch_bounds__(256)
-causal_conv_kernel(const T* __restrict__ in, T* __restrict__ out, long long ld, int col0, int C,
+causal_conv_norm_kernel(const T* __restrict__ in, T* __restrict__ out, long long ld, long long out_ld, int col0, int C,
+                        const float* __restrict__ taps, int n, const float* __restrict__ state, long long slot_stride,
+                        const int* __restrict__ tok_seg, const int* __restrict__ seg_start,
+                        const int* __restrict__ seg_slot, ConvNormRange r0, ConvNormRange r1, float eps) {
+    fwb::pdl_entry();
+    extern __shared__ float row[];                 // [C]
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int seg = tok_seg[t];
+    const int local = t - seg_start[seg];
+    const float* slot = state + (size_t)seg_slot[seg] * slot_stride;
+    float ss0 = 0.0f, ss1 = 0.0f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const float v = conv_one<T>(in, (size_t)t * ld + col0 + c, ld, taps, n, c, C, local, slot);
+        row[c] = v;
+        if (c >= r0.col0 && c < r0.col0 + r0.width) ss0 = fmaf(v, v, ss0);
+        else if (c >= r1.col0 && c < r1.col0 + r1.width) ss1 = fmaf(v, v, ss1);
+    }
+    const float inv0 = rsqrtf(block_sum(ss0, scratch) / (float)(r0.count > 0 ? r0.count : 1) + eps);
+    const float inv1 = r1.width > 0 ? rsqrtf(block_sum(ss1, scratch) / (float)(r1.count > 0 ? r1.count : 1) + eps) : 0.0f;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float v = row[c];
+        if (c >= r0.col0 && c < r0.col0 + r0.width) v = (v * inv0) * r0.weight[c - r0.col0];
+        else if (c >= r1.col0 && c < r1.col0 + r1.width) v = (v * inv1) * r1.weight[c - r1.col0];
+        out[(size_t)t * out_ld + c] = from_f32<T>(v);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const T* __restrict__ in, T* __restrict__ out, long long ld, long long out_ld, int col0, int C,
                    const float* __restrict__ taps, int n, const float* __restrict__ state, long long slot_stride,
                    const int* __restrict__ tok_seg, const int* __restrict__ seg_start,
                    const int* __restrict__ seg_slot) {
@@ -33,15 +89,8 @@ causal_conv_kernel(const T* __restrict__ in, T* __restrict__ out, long long ld, 
     const int seg = tok_seg[t];
     const int local = t - seg_start[seg];                 // tokens of this segment in front of t
     const float* slot = state + (size_t)seg_slot[seg] * slot_stride;
-    float acc = 0.0f;
-    for (int j = 0; j < n; ++j) {
-        const int back = n - 1 - j;                        // how far behind t this tap reads
-        float u;
-        if (back <= local) u = to_f32<T>(in[(size_t)(t - back) * ld + col0 + c]);
-        else u = slot[(size_t)(n - 1 + local - back) * C + c];   // state row n-1-(back-local)
-        acc = fmaf(taps[(size_t)c * n + j], u, acc);
-    }
-    out[(size_t)t * ld + col0 + c] = from_f32<T>(acc);
+    const float acc = conv_one<T>(in, (size_t)t * ld + col0 + c, ld, taps, n, c, C, local, slot);
+    out[(size_t)t * out_ld + c] = from_f32<T>(acc);
 }
 
 // One thread per (segment, channel): the new state rows are the segment's last n - 1 inputs, or, for a
@@ -67,12 +116,21 @@ causal_conv_advance_kernel(const T* __restrict__ in, long long ld, int col0, int
 }
 
 template <typename T>
-int launch(const void* in, void* out, long long ld, int col0, int C, const float* taps, int n, float* state,
-           long long slot_stride, const int* tok_seg, const int* seg_start, const int* seg_slot, int T_tokens,
-           int S, cudaStream_t stream) {
-    const dim3 grid(T_tokens, (C + 255) / 256);
-    fwb::pdl(causal_conv_kernel<T>, grid, 256, 0, stream)((const T*)in, (T*)out, ld, col0, C, taps, n, state,
-                                                          slot_stride, tok_seg, seg_start, seg_slot);
+int launch(const void* in, void* out, long long ld, long long out_ld, int col0, int C, const float* taps, int n,
+           float* state, long long slot_stride, const int* tok_seg, const int* seg_start, const int* seg_slot,
+           int T_tokens, int S, ConvNormRange r0, ConvNormRange r1, float eps, cudaStream_t stream) {
+    if (r0.width > 0) {
+        const size_t smem = (size_t)C * sizeof(float);
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(causal_conv_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fwb::pdl(causal_conv_norm_kernel<T>, T_tokens, 256, smem, stream)(
+            (const T*)in, (T*)out, ld, out_ld, col0, C, taps, n, state, slot_stride, tok_seg, seg_start, seg_slot, r0,
+            r1, eps);
+    } else {
+        const dim3 grid(T_tokens, (C + 255) / 256);
+        fwb::pdl(causal_conv_kernel<T>, grid, 256, 0, stream)((const T*)in, (T*)out, ld, out_ld, col0, C, taps, n,
+                                                              state, slot_stride, tok_seg, seg_start, seg_slot);
+    }
     if (n > 1) {
         const dim3 grid2(S, (C + 255) / 256);
         fwb::pdl(causal_conv_advance_kernel<T>, grid2, 256, 0, stream)((const T*)in, ld, col0, C, n, state,
@@ -83,19 +141,31 @@ int launch(const void* in, void* out, long long ld, int col0, int C, const float
 
 }  // namespace
 
-// in, out: [T][ld] fp32 or bf16 (both of one type, different buffers); taps: [C][n] fp32; state: fp32, slot s
-// at state + s * slot_stride, [n - 1][C] (may be null when n == 1); tok_seg: [T]; seg_start: [S + 1];
-// seg_slot: [S].
-FWB_API int fwb_causal_conv(const void* in, void* out, int is_bf16, long long ld, int col0, int C,
+// in: [T][ld], out: [T][out_ld], fp32 or bf16 (both of one type, different buffers); taps: [C][n] fp32; state: fp32,
+// slot s at state + s * slot_stride, [n - 1][C] (may be null when n == 1); tok_seg: [T]; seg_start: [S + 1];
+// seg_slot: [S].  Norm ranges (width0 == 0: none; width1 == 0: one): columns [c0, c0 + width) of the output, the
+// mean of squares over `count` channels, weights fp32 [width].
+FWB_API int fwb_causal_conv(const void* in, void* out, int is_bf16, long long ld, long long out_ld, int col0, int C,
                             const float* taps, int n, float* state, long long slot_stride, const int* tok_seg,
-                            const int* seg_start, const int* seg_slot, int T, int S, cudaStream_t stream) {
+                            const int* seg_start, const int* seg_slot, int T, int S, int norm_col0, int norm_width0,
+                            int norm_count0, const float* norm_w0, int norm_col1, int norm_width1, int norm_count1,
+                            const float* norm_w1, float eps, cudaStream_t stream) {
     if (T <= 0 || C <= 0) return FWB_OK;
     if (!in || !out || in == out || !taps || !tok_seg || !seg_start || !seg_slot || n < 1 || S <= 0 || col0 < 0 ||
-        ld < col0 + C || (n > 1 && !state))
+        ld < col0 + C || out_ld < C || (n > 1 && !state))
         return FWB_BAD_ARGUMENT;
     if (n > MAX_TAPS || (C + 255) / 256 > 65535) return FWB_TOO_LARGE;
-    return is_bf16 ? launch<__nv_bfloat16>(in, out, ld, col0, C, taps, n, state, slot_stride, tok_seg, seg_start,
-                                           seg_slot, T, S, stream)
-                   : launch<float>(in, out, ld, col0, C, taps, n, state, slot_stride, tok_seg, seg_start, seg_slot,
-                                   T, S, stream);
+    ConvNormRange r0{norm_col0, norm_width0, norm_count0, norm_w0}, r1{norm_col1, norm_width1, norm_count1, norm_w1};
+    if (r0.width > 0) {
+        if (!r0.weight || r0.col0 < 0 || r0.col0 + r0.width > C || (r1.width > 0 && (!r1.weight || r1.col0 < 0 ||
+                                                                                      r1.col0 + r1.width > C)))
+            return FWB_BAD_ARGUMENT;
+        if ((size_t)C * sizeof(float) > 160 * 1024) return FWB_TOO_LARGE;
+    } else if (r1.width > 0) {
+        return FWB_BAD_ARGUMENT;
+    }
+    return is_bf16 ? launch<__nv_bfloat16>(in, out, ld, out_ld, col0, C, taps, n, state, slot_stride, tok_seg, seg_start,
+                                           seg_slot, T, S, r0, r1, eps, stream)
+                   : launch<float>(in, out, ld, out_ld, col0, C, taps, n, state, slot_stride, tok_seg, seg_start,
+                                   seg_slot, T, S, r0, r1, eps, stream);
 }

@@ -60,15 +60,18 @@ __global__ void value_mix_kernel(T* __restrict__ rows, long long row_stride, int
     }
 }
 
-template <typename T>
-__global__ void sigmoid_gate_mul_kernel(T* __restrict__ y, const T* __restrict__ gate, int n_rows, int heads,
-                                        int head_dim, int gate_width) {
+// gate rows are `gate_stride` entries apart (heads * gate_width of them in use)
+template <typename T, typename TG>
+__global__ void sigmoid_gate_mul_kernel(T* __restrict__ y, const TG* __restrict__ gate, long long gate_stride,
+                                        int n_rows, int heads, int head_dim, int gate_width) {
     fwb::pdl_entry();
     const size_t n = (size_t)n_rows * heads * head_dim;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t th = i / head_dim;
         const int c = (int)(i - th * head_dim);
-        const float g = to_f32<T>(gate[th * gate_width + (gate_width == 1 ? 0 : c)]);
+        const size_t t = th / heads;
+        const int h = (int)(th - t * heads);
+        const float g = to_f32<TG>(gate[t * gate_stride + (size_t)h * gate_width + (gate_width == 1 ? 0 : c)]);
         y[i] = from_f32<T>(to_f32<T>(y[i]) * sigmoid_f32(g));
     }
 }
@@ -211,8 +214,29 @@ FWB_API int fwb_sigmoid_gate_mul(void* y, const void* gate, int is_bf16, int T, 
     if (T <= 0) return FWB_OK;
     if (!y || !gate || heads <= 0 || head_dim <= 0 || (gate_width != 1 && gate_width != head_dim)) return FWB_BAD_ARGUMENT;
     const int blocks = blocks_for((size_t)T * heads * head_dim);
-    if (is_bf16) fwb::pdl(sigmoid_gate_mul_kernel<bf>, blocks, 256, 0, stream)((bf*)y, (const bf*)gate, T, heads, head_dim, gate_width);
-    else fwb::pdl(sigmoid_gate_mul_kernel<float>, blocks, 256, 0, stream)((float*)y, (const float*)gate, T, heads, head_dim, gate_width);
+    const long long stride = (long long)heads * gate_width;
+    if (is_bf16) fwb::pdl(sigmoid_gate_mul_kernel<bf, bf>, blocks, 256, 0, stream)((bf*)y, (const bf*)gate, stride, T, heads, head_dim, gate_width);
+    else fwb::pdl(sigmoid_gate_mul_kernel<float, float>, blocks, 256, 0, stream)((float*)y, (const float*)gate, stride, T, heads, head_dim, gate_width);
+    return fwb_launch_status();
+}
+
+// The same with the gate inside the rows of another buffer (some columns of a fused projection): `gate` points at
+// the first gate entry of row 0, rows are `gate_stride` entries apart, and its type may differ from y's.
+FWB_API int fwb_sigmoid_gate_mul_strided(void* y, int y_bf16, const void* gate, int gate_bf16, long long gate_stride,
+                                         int T, int heads, int head_dim, int gate_width, cudaStream_t stream) {
+    if (T <= 0) return FWB_OK;
+    if (!y || !gate || heads <= 0 || head_dim <= 0 || (gate_width != 1 && gate_width != head_dim) ||
+        gate_stride < (long long)heads * gate_width)
+        return FWB_BAD_ARGUMENT;
+    const int blocks = blocks_for((size_t)T * heads * head_dim);
+    if (y_bf16 && gate_bf16)
+        fwb::pdl(sigmoid_gate_mul_kernel<bf, bf>, blocks, 256, 0, stream)((bf*)y, (const bf*)gate, gate_stride, T, heads, head_dim, gate_width);
+    else if (y_bf16)
+        fwb::pdl(sigmoid_gate_mul_kernel<bf, float>, blocks, 256, 0, stream)((bf*)y, (const float*)gate, gate_stride, T, heads, head_dim, gate_width);
+    else if (!gate_bf16)
+        fwb::pdl(sigmoid_gate_mul_kernel<float, float>, blocks, 256, 0, stream)((float*)y, (const float*)gate, gate_stride, T, heads, head_dim, gate_width);
+    else
+        return FWB_UNSUPPORTED;
     return fwb_launch_status();
 }
 

@@ -424,7 +424,8 @@ template <typename TH>
 __global__ void __launch_bounds__(256)
 moe_combine_norm_add_kernel(const float* __restrict__ y, const TH* __restrict__ h, const int* __restrict__ pair_row,
                             const int* __restrict__ ids, const float* __restrict__ weights, float* __restrict__ x,
-                            const float* __restrict__ norm_w, float eps, int W, int top, int E) {
+                            const float* __restrict__ norm_w, float eps, int W, int top, int E,
+                            const float* __restrict__ extra) {
     fwb::pdl_entry();
     constexpr int MAX_TOP = 64;
     extern __shared__ float sum_row[];            // [W]
@@ -454,6 +455,10 @@ moe_combine_norm_add_kernel(const float* __restrict__ y, const TH* __restrict__ 
                 acc.x = fmaf(wt, v.x, acc.x), acc.y = fmaf(wt, v.y, acc.y);
                 acc.z = fmaf(wt, v.z, acc.z), acc.w = fmaf(wt, v.w, acc.w);
             }
+            if (extra) {                               // (what every token gets besides its experts: added last)
+                const float4 more = reinterpret_cast<const float4*>(extra)[(size_t)t * (W / 4) + i];
+                acc.x += more.x, acc.y += more.y, acc.z += more.z, acc.w += more.w;
+            }
             reinterpret_cast<float4*>(sum_row)[i] = acc;
             ss = fmaf(acc.x, acc.x, fmaf(acc.y, acc.y, fmaf(acc.z, acc.z, fmaf(acc.w, acc.w, ss))));
         }
@@ -466,6 +471,7 @@ moe_combine_norm_add_kernel(const float* __restrict__ y, const TH* __restrict__ 
                 const float v = row >= 0 ? y[(size_t)row * W + i] : (row == -1 ? own : 0.0f);
                 acc = fmaf(wts[slot], v, acc);
             }
+            if (extra) acc += extra[(size_t)t * W + i];
             sum_row[i] = acc;
             ss = fmaf(acc, acc, ss);
         }
@@ -578,10 +584,11 @@ FWB_API int fwb_moe_combine(const float* y, const void* h, int h_bf16, const int
     return fwb_launch_status();
 }
 
-// The same sum, then x[t] += norm_w * sum / sqrt(mean(sum^2) + eps) in place (x: [T][W] fp32).
+// The same sum (plus row t of `extra`, fp32 [T][W] or null: what every token gets besides its experts), then
+// x[t] += norm_w * sum / sqrt(mean(sum^2) + eps) in place (x: [T][W] fp32).
 FWB_API int fwb_moe_combine_norm_add(const float* y, const void* h, int h_bf16, const int* pair_row, const int* ids,
                                      const float* weights, float* x, const float* norm_w, float eps, int T, int W,
-                                     int top, int E, cudaStream_t stream) {
+                                     int top, int E, const float* extra, cudaStream_t stream) {
     if (T <= 0) return FWB_OK;
     if (!y || !h || !pair_row || !ids || !weights || !x || !norm_w || W <= 0 || top <= 0) return FWB_BAD_ARGUMENT;
     if (top > 64) return FWB_TOO_LARGE;
@@ -591,12 +598,12 @@ FWB_API int fwb_moe_combine_norm_add(const float* y, const void* h, int h_bf16, 
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(moe_combine_norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         fwb::pdl(moe_combine_norm_add_kernel<__nv_bfloat16>, T, 256, smem, stream)(
-            y, (const __nv_bfloat16*)h, pair_row, ids, weights, x, norm_w, eps, W, top, E);
+            y, (const __nv_bfloat16*)h, pair_row, ids, weights, x, norm_w, eps, W, top, E, extra);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(moe_combine_norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         fwb::pdl(moe_combine_norm_add_kernel<float>, T, 256, smem, stream)(y, (const float*)h, pair_row, ids, weights, x,
-                                                                           norm_w, eps, W, top, E);
+                                                                           norm_w, eps, W, top, E, extra);
     }
     return fwb_launch_status();
 }

@@ -56,7 +56,8 @@ def experts_forward(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
     rows), ``w_down``: [E][W][F], both in the dtype of ``h``.  Router outputs from E on are identity
     experts: they pass ``h`` itself on.  ``add_normed_into`` = (x, norm weight, eps): the sum is not
     returned but normed and added, ``x += weight * sum / sqrt(mean(sum^2) + eps)`` in fp32, by the kernel
-    that makes it (returns None)."""
+    that makes it (returns None); a fourth entry, fp32 [T][W], is added to every token's sum first (the output of an
+    expert that every token shares)."""
     check_tensor("expert input", h)
     T, W = h.shape
     top = ids.shape[1]
@@ -100,11 +101,14 @@ def experts_forward(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w
         lib.call("fwb_moe_gemm", ptr(a), ptr(w_down), bf16, ptr(y), ptr(offsets), ptr(row_token), ptr(tiles),
                  max_tiles, W, F, 0, 0, c_float(0.0), stream())
     if add_normed_into is not None:
-        x, norm_weight, eps = add_normed_into
+        x, norm_weight, eps = add_normed_into[:3]
+        extra = add_normed_into[3] if len(add_normed_into) > 3 else None
         check_tensor("residual", x, torch.float32, (T, W))
         check_tensor("norm weight", norm_weight, torch.float32, (W,))
+        if extra is not None:
+            check_tensor("shared output", extra, torch.float32, (T, W))
         lib.call("fwb_moe_combine_norm_add", ptr(y), ptr(h), bf16, ptr(pair_row), ptr(ids), ptr(weights), ptr(x),
-                 ptr(norm_weight), c_float(eps), T, W, top, E, stream())
+                 ptr(norm_weight), c_float(eps), T, W, top, E, ptr(extra), stream())
         return None
     out = torch.empty((T, W), dtype=torch.float32, device=dev)
     lib.call("fwb_moe_combine", ptr(y), ptr(h), bf16, ptr(pair_row), ptr(ids), ptr(weights), ptr(out), T, W, top,

@@ -42,25 +42,42 @@ def rmsnorm_ranges_(buf: torch.Tensor, ranges) -> torch.Tensor:
     return buf
 
 
-def causal_conv(rows: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tensor], batch) -> torch.Tensor:
-    """A causal convolution over time on every channel of ``rows`` ([T][C], fp32 or bf16), ``taps`` fp32 [C][n]
-    with the last tap on the token itself: ``y[t] = sum_j taps[:, j] * rows[t - n + 1 + j]`` along each
+def causal_conv(rows: torch.Tensor, taps: torch.Tensor, state: Optional[torch.Tensor], batch,
+                norm_ranges=None) -> torch.Tensor:
+    """A causal convolution over time on the first C channels of ``rows`` ([T][>= C], fp32 or bf16), ``taps`` fp32
+    [C][n] with the last tap on the token itself: ``y[t] = sum_j taps[:, j] * rows[t - n + 1 + j]`` along each
     request's tokens.  ``state``: fp32 [slots][n - 1][C], every live request's last n - 1 inputs (zero when it
-    starts), read in front of a portion and moved on by this call (None when n == 1).  Returns a new buffer."""
+    starts), read in front of a portion and moved on by this call (None when n == 1).  ``norm_ranges``: one or two
+    ``(col0, weight, count, eps)`` as ``rmsnorm_ranges_`` takes them; those column ranges of the result are
+    normed by the same launch.  Returns a new buffer [T][C]; ``rows`` (and its columns from C on) stay."""
     check_tensor("convolution input", rows)
-    T, C = rows.shape
-    n = taps.shape[1]
-    check_tensor("convolution taps", taps, torch.float32, (C, n))
+    T, ld = rows.shape
+    C, n = taps.shape
+    check_tensor("convolution taps", taps, torch.float32)
+    if C > ld:
+        raise KernelError(f"taps for {C} channels, rows of {ld}")
     stride = 0
     if n > 1:
         if state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (n - 1, C) \
                 or state.stride(2) != 1 or state.stride(1) != C:
             raise KernelError(f"the convolution's state must be fp32 [slots][{n - 1}][{C}] with contiguous slots")
         stride = state.stride(0) if state.shape[0] > 1 else (n - 1) * C
-    out = torch.empty_like(rows)
-    lib.call("fwb_causal_conv", ptr(rows), ptr(out), is_bf16(rows), c_longlong(C), 0, C, ptr(taps), n,
+    norm_args = [0, 0, 0, None, 0, 0, 0, None]
+    eps = 0.0
+    if norm_ranges:
+        if not 1 <= len(norm_ranges) <= 2 or C * 4 > 160 * 1024:
+            raise KernelError("the convolution norms one or two column ranges of rows of at most 40,960 channels")
+        eps = float(norm_ranges[0][3])
+        for index, (col0, weight, count, this_eps) in enumerate(norm_ranges):
+            check_tensor("range norm weight", weight, torch.float32)
+            if float(this_eps) != eps:
+                raise KernelError("the ranges of one launch share their eps")
+            norm_args[4 * index:4 * index + 4] = [int(col0), weight.numel(), int(count), ptr(weight)]
+    out = torch.empty((T, C), dtype=rows.dtype, device=rows.device)
+    lib.call("fwb_causal_conv", ptr(rows), ptr(out), is_bf16(rows), c_longlong(ld), c_longlong(C), 0, C, ptr(taps), n,
              ptr(state) if n > 1 else None, c_longlong(stride), ptr(batch.tok_seg), ptr(batch.seg_start),
-             ptr(batch.seg_slot), T, batch.n_segments, stream(), launches=2 if n > 1 else 1)
+             ptr(batch.seg_slot), T, batch.n_segments, *norm_args, c_float(eps), stream(),
+             launches=2 if n > 1 else 1)
     return out
 
 
@@ -93,6 +110,21 @@ def sigmoid_gate_mul_(y: torch.Tensor, gate: torch.Tensor, heads: int, head_dim:
     else:
         raise KernelError(f"a gate of {width} entries per token fits neither {heads} heads nor their channels")
     lib.call("fwb_sigmoid_gate_mul", ptr(y), ptr(gate), is_bf16(y), T, heads, head_dim, per_head, stream())
+    return y
+
+
+def sigmoid_gate_cols_mul_(y: torch.Tensor, rows: torch.Tensor, col0: int, heads: int, head_dim: int) -> torch.Tensor:
+    """``y[t][h][c] *= sigmoid(rows[t][col0 + h])``: a gate per head that lies in columns of another buffer (a
+    fused projection's last columns), of its own dtype; in place."""
+    check_tensor("attention output", y)
+    check_tensor("projection rows", rows)
+    T = y.shape[0]
+    if y.numel() != T * heads * head_dim or rows.shape[0] != T or col0 + heads > rows.shape[1]:
+        raise KernelError("the gated rows and the gate's columns do not fit")
+    if rows.dtype == torch.bfloat16 and y.dtype != torch.bfloat16:
+        raise KernelError("a 16-bit gate on 32-bit rows has no kernel")
+    lib.call("fwb_sigmoid_gate_mul_strided", ptr(y), is_bf16(y), rows.data_ptr() + col0 * rows.element_size(),
+             is_bf16(rows), c_longlong(rows.shape[1]), T, heads, head_dim, 1, stream())
     return y
 
 

@@ -102,6 +102,9 @@ class GQAttention(Mixer):
         # the head kernel reads them: one rounding, not two.  (Mixed values are rounded on both sides of the
         # mix in 16-bit runs: what the products' dtype means for a projection and for a cached value.)
         self._wide_qkv = self.qk_norm == "whole"
+        # a gate per head behind a convolution: its rows ride in the q|k|v product (the convolution writes a
+        # buffer of its own, so the gate's columns stay where the product left them)
+        self._gate_in_projection = self.gate == "head" and self.conv_taps > 0
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.w_gate = self.sink = self.vmix = None
         self.taps = None
 
@@ -150,10 +153,15 @@ class GQAttention(Mixer):
         mats = [rows_padded(get(n["q"]), self.qk_dim)]
         if not self.shares_cache:
             mats += [rows_padded(get(n["k"]), self.qk_dim), rows_padded(get(n["v"]), self.value_dim)]
+        self._qkv_columns = sum(m.shape[0] for m in mats)
+        if self._gate_in_projection:
+            gate_rows = get(n["g"])
+            pad = -gate_rows.shape[0] % 8                     # (a row count the products' tiles like)
+            mats += [gate_rows] + ([gate_rows.new_zeros((pad, gate_rows.shape[1]))] if pad else [])
         dtypes = {m.dtype for m in mats}
         if len(dtypes) > 1:
             mats = [m.to(torch.float32) for m in mats]
-        # one projection for q|k|v: the rows of the three matrices, one after the other
+        # one projection for q|k|v (|gate): the rows of the matrices, one after the other
         self.w_qkv = precision.matrix(torch.cat(mats, dim=0), device)
         w_o = get(n["o"])
         if self.value_dim != D:                   # zero columns where the padded channels of a head arrive
@@ -182,7 +190,7 @@ class GQAttention(Mixer):
             if not self.shares_cache:
                 taps += [rows_padded(get(n["k_conv"]), self.qk_dim), rows_padded(get(n["v_conv"]), self.value_dim)]
             self.taps = precision.vector(torch.cat([t.to(torch.float32) for t in taps], dim=0), device)
-        if self.gate:
+        if self.gate and not self._gate_in_projection:
             w_gate = get(n["g"])
             self.w_gate = precision.matrix(rows_padded(w_gate, self.value_dim) if self.gate == "element" else w_gate,
                                            device)
@@ -268,13 +276,21 @@ class GQAttention(Mixer):
         qkv = ops.linear(h, self.w_qkv, torch.float32 if self._wide_qkv else act)
         block_table = ctx.batch.block_tables[cache.group]
         k_at, v_at = self.n_heads * D, (self.n_heads + self._kv_in) * D
-        if self.conv_taps:
-            qkv = mixing.causal_conv(qkv, self.taps, cache.state if self.conv_taps > 1 else None, ctx.batch)
         whole = self.qk_norm == "whole"
+        ranges = None
         if whole:
             ranges = [(0, self.q_norm, self.n_heads * self.qk_dim, self.eps)]
             if self._kv_in:
                 ranges.append((k_at, self.k_norm, self.n_kv * self.qk_dim, self.eps))
+        projected = qkv
+        if self.conv_taps:
+            # the convolution (and the norm over the whole of q and of k behind it, in the same launch)
+            fused = ranges if self._qkv_columns * 4 <= 160 * 1024 else None
+            qkv = mixing.causal_conv(projected, self.taps, cache.state if self.conv_taps > 1 else None, ctx.batch,
+                                     norm_ranges=fused)
+            if fused is not None:
+                ranges = None
+        if ranges is not None:
             mixing.rmsnorm_ranges_(qkv, ranges)
         if self.value_mix == "source":
             first = torch.empty((qkv.shape[0], self.n_kv * D), dtype=qkv.dtype, device=qkv.device)
@@ -293,7 +309,9 @@ class GQAttention(Mixer):
                                  cache=cache, block_table=block_table, **extra)
         out = attention_kernels.paged_attention(ctx, q, cache, block_table, self.n_heads, self.span, self.scale,
                                                 act, sink=self.sink, softcap=self.softcap)
-        if self.gate:
+        if self._gate_in_projection:
+            mixing.sigmoid_gate_cols_mul_(out, projected, self._qkv_columns, self.n_heads, D)
+        elif self.gate:
             mixing.sigmoid_gate_mul_(out, ops.linear(h, self.w_gate, act), self.n_heads, D)
         return ops.linear_into_residual(out, self.w_o, residual)
 

@@ -91,9 +91,14 @@ class LatentAttention(Mixer):
     def bind(self, get, precision: Precision, device):
         n = self.names
         mats = [get(n["q"])] + ([] if self.shares_cache else [get(n["dkv"])])
+        self._gate_col = sum(m.shape[0] for m in mats)
+        if self.gate:
+            gate_rows = get(n["g"])
+            pad = -(self._gate_col + gate_rows.shape[0]) % 8  # (a row count the products' tiles like)
+            mats += [gate_rows] + ([gate_rows.new_zeros((pad, gate_rows.shape[1]))] if pad else [])
         if len({m.dtype for m in mats}) > 1:
             mats = [m.to(torch.float32) for m in mats]
-        # one projection for the queries and the latent: the rows of the two matrices, one after the other
+        # one projection for the queries, the latent and the gates: the rows of the matrices, one after the other
         self.w_in = precision.matrix(torch.cat(mats, dim=0), device)
         # U as [heads][rank][dim]: the product that carries a plain query into the latent's space
         uk = get(n["uk"]).reshape(self.n_heads, self.dim, self.rank).transpose(1, 2)
@@ -104,8 +109,6 @@ class LatentAttention(Mixer):
             self.norm_w = precision.vector(get(n["dkv_norm"]), device)
         if self.has_sink:
             self.sink = precision.vector(get(n["sink"]), device)
-        if self.gate:
-            self.w_gate = precision.matrix(get(n["g"]), device)
 
     def _matrices(self):
         return tuple(m for m in (self.w_in, self.w_uk_t, self.w_uv, self.w_o, self.w_gate) if m is not None)
@@ -183,5 +186,5 @@ class LatentAttention(Mixer):
         latent_kernels.head_linear(mixed, 0, stride, self.rank, self.w_uv, heads_out, 0, self.vdim)
         if self.gate:
             from ..kernels import mixing
-            mixing.sigmoid_gate_mul_(heads_out, ops.linear(h, self.w_gate, act), self.n_heads, self.vdim)
+            mixing.sigmoid_gate_cols_mul_(heads_out, proj, self._gate_col, self.n_heads, self.vdim)
         return ops.linear(heads_out, self.w_o, torch.float32)

@@ -211,3 +211,14 @@ class TableExperts(FeedForward):
             if rest is not None:
                 ops.add_(out, rest)
         return out
+
+    def forward_add_normed(self, ctx, h, x, norm_weight, eps):
+        """``x += norm_weight * unit(ff(h))``: the shared expert first, then the experts' weighted sum, the shared
+        output, the output norm and the residual sum in one kernel."""
+        shared = None
+        if self.shared_ffn:
+            shared = ops.linear(self._shared_hidden(ctx, h), self.shared_down, torch.float32)
+        ids, weights = expert_kernels.route_table(ctx.batch.token_ids, self.table, self.top)
+        rows = h if h.dtype == self.w_gate_up.dtype else ops.cast(h, self.w_gate_up.dtype)
+        expert_kernels.experts_forward(rows, ids, weights, self.w_gate_up, self.w_down, self.activation,
+                                       add_normed_into=(x, norm_weight, eps, shared), limit=self.limit)

@@ -89,6 +89,61 @@ def test_causal_convolution_over_portions_single_tokens_and_shuffled_slots(dtype
         assert torch.isnan(state[4]).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("taps,q,k,v,pad", [(3, 40, 24, 16, 0), (1, 64, 0, 0, 0), (4, 18, 6, 10, 8), (2, 3072, 512, 512, 40)])
+def test_convolution_with_the_norm_over_ranges_and_columns_it_leaves_alone(dtype, taps, q, k, v, pad):
+    """The convolution that also norms the q range and the k range of its output (the mean over fewer channels
+    than a range is wide: the last two of each count as padding), from rows that carry ``pad`` more columns
+    behind the convolved ones; two portions of one sequence beside a second sequence."""
+    from flyweight_b200.engine import Segment, StepBatch
+    from flyweight_b200.kernels import mixing
+    g = torch.Generator().manual_seed(q + taps)
+    C = q + k + v
+    rnd = rounding(dtype)
+    rows = [rnd(torch.randn(n, C + pad, generator=g, dtype=F64).float().to(F64)) for n in (70, 9)]
+    w = torch.randn(C, taps, generator=g, dtype=F64).float().to(F64)
+    wq, wk = (1.0 + 0.2 * torch.randn(n, generator=g, dtype=F64)).float().to(F64), None
+    ranges = [(0, dev(wq.float()), q - 2, EPS)]
+    if k:
+        wk = (1.0 + 0.2 * torch.randn(k, generator=g, dtype=F64)).float().to(F64)
+        ranges.append((q, dev(wk.float()), k - 2, EPS))
+    want = []
+    for r in rows:
+        y = P.causal_taps(r[:, :C], w)
+        y[:, :q] = y[:, :q] / torch.sqrt((y[:, :q] ** 2).sum(-1, keepdim=True) / (q - 2) + EPS) * wq
+        if k:
+            y[:, q:q + k] = y[:, q:q + k] / torch.sqrt((y[:, q:q + k] ** 2).sum(-1, keepdim=True) / (k - 2) + EPS) * wk
+        want.append(y)
+    state = torch.zeros((2, taps - 1, C), dtype=torch.float32, device=DEV) if taps > 1 else None
+    got = [[], []]
+    done = [0, 0]
+    for step in ([(0, 33), (1, 2)], [(1, 7), (0, 37)]):
+        batch = StepBatch([Segment(f"s{s}", 1 - s, done[s], [0] * m, []) for s, m in step], [[[0]] * 2], DEV)
+        u = dev(torch.cat([rows[s][done[s]:done[s] + m] for s, m in step]).to(dtype))
+        y = mixing.causal_conv(u, dev(w.float()), state, batch, norm_ranges=ranges)
+        assert tuple(y.shape) == (u.shape[0], C)
+        at = 0
+        for s, m in step:
+            got[s].append(y[at:at + m].float().cpu())
+            at += m
+            done[s] += m
+    for s in range(2):
+        close(torch.cat(got[s]), want[s], 1e-5 if dtype == torch.float32 else 1.5e-2, f"sequence {s}")
+
+
+def test_a_gate_per_head_from_columns_of_another_buffer():
+    from flyweight_b200.kernels import mixing
+    g = torch.Generator().manual_seed(1)
+    T, heads, d = 19, 5, 12
+    y = torch.randn(T, heads * d, generator=g, dtype=F64).float().to(F64)
+    rows = torch.randn(T, 31, generator=g, dtype=F64).float().to(F64) * 3.0
+    want = (y.view(T, heads, d) * torch.sigmoid(rows[:, 20:20 + heads])[:, :, None]).reshape(T, -1)
+    for y_dtype, rows_dtype, tol in ((torch.float32, torch.float32, 1e-6), (torch.bfloat16, torch.float32, 1e-2),
+                                     (torch.bfloat16, torch.bfloat16, 2e-2)):
+        got = mixing.sigmoid_gate_cols_mul_(dev(y.to(y_dtype)), dev(rows.to(rows_dtype)), 20, heads, d)
+        close(got, want, tol, f"{y_dtype} rows gated from {rows_dtype} columns")
+
+
 # ------------------------------------------------------------------ the clamped swish on gate and up
 def plain_gated(g, u, limit):
     g = torch.clamp(g, max=limit)
@@ -387,6 +442,12 @@ def test_experts_by_table_with_a_shared_expert(dtype, tensor_cores, mlp, width):
         expert_kernels.set_tensor_cores(True)
     want = P.table_experts(h, tokens, w, "l0.mlp.", raw["layers"][0]["mlp"], rnd=rnd)
     close(got, want, TOL[dtype], "experts")
+    # the same with the output norm and the residual sum in the kernel that adds the experts up
+    x0 = torch.randn(150, width, generator=g, dtype=F64).float().to(F64)
+    norm_w = (1.0 + 0.2 * torch.randn(width, generator=g, dtype=F64)).float().to(F64)
+    x = dev(x0.float())
+    ff.forward_add_normed(ctx, dev(rnd(h).to(precision.act_dtype)), x, dev(norm_w.float()), EPS)
+    close(x, x0 + P.unit(want, EPS) * norm_w, TOL[dtype], "experts, normed and added")
     loose = {"kind": "moe", "expert": {"ff": mlp[0], "limit": 50.0}, "router": raw["layers"][0]["mlp"]["router"]}
     if mlp[4]:
         loose["shared"] = {"ff": mlp[4][0], "limit": 50.0}
