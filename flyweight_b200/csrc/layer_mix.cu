@@ -220,6 +220,26 @@ FWB_API int fwb_sigmoid_gate_mul(void* y, const void* gate, int is_bf16, int T, 
     return fwb_launch_status();
 }
 
+// bfloat16 rows, eight entries (16 bytes) a thread and turn, a gate per head: one sigmoid for the eight.
+template <typename TG>
+__global__ void sigmoid_head_gate_mul_bf16x8_kernel(uint4* __restrict__ y, const TG* __restrict__ gate, long long gate_stride,
+                                                    size_t n8, int heads, int head_dim8) {
+    fwb::pdl_entry();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t th = i / head_dim8;
+        const size_t t = th / heads;
+        const float s = sigmoid_f32(to_f32<TG>(gate[t * gate_stride + (th - t * heads)]));
+        uint4 raw = y[i];
+        __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 v = __bfloat1622float2(pairs[j]);
+            pairs[j] = __floats2bfloat162_rn(v.x * s, v.y * s);
+        }
+        y[i] = raw;
+    }
+}
+
 // The same with the gate inside the rows of another buffer (some columns of a fused projection): `gate` points at
 // the first gate entry of row 0, rows are `gate_stride` entries apart, and its type may differ from y's.
 FWB_API int fwb_sigmoid_gate_mul_strided(void* y, int y_bf16, const void* gate, int gate_bf16, long long gate_stride,
@@ -229,6 +249,14 @@ FWB_API int fwb_sigmoid_gate_mul_strided(void* y, int y_bf16, const void* gate, 
         gate_stride < (long long)heads * gate_width)
         return FWB_BAD_ARGUMENT;
     const int blocks = blocks_for((size_t)T * heads * head_dim);
+    if (y_bf16 && gate_width == 1 && head_dim % 8 == 0 && ((uintptr_t)y & 15) == 0) {
+        const size_t n8 = (size_t)T * heads * (head_dim / 8);
+        if (gate_bf16)
+            fwb::pdl(sigmoid_head_gate_mul_bf16x8_kernel<bf>, blocks_for(n8), 256, 0, stream)((uint4*)y, (const bf*)gate, gate_stride, n8, heads, head_dim / 8);
+        else
+            fwb::pdl(sigmoid_head_gate_mul_bf16x8_kernel<float>, blocks_for(n8), 256, 0, stream)((uint4*)y, (const float*)gate, gate_stride, n8, heads, head_dim / 8);
+        return fwb_launch_status();
+    }
     if (y_bf16 && gate_bf16)
         fwb::pdl(sigmoid_gate_mul_kernel<bf, bf>, blocks, 256, 0, stream)((bf*)y, (const bf*)gate, gate_stride, T, heads, head_dim, gate_width);
     else if (y_bf16)

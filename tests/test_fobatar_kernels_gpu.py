@@ -102,7 +102,7 @@ def test_convolution_with_the_norm_over_ranges_and_columns_it_leaves_alone(dtype
     rnd = rounding(dtype)
     rows = [rnd(torch.randn(n, C + pad, generator=g, dtype=F64).float().to(F64)) for n in (70, 9)]
     w = torch.randn(C, taps, generator=g, dtype=F64).float().to(F64)
-    wq, wk = (1.0 + 0.2 * torch.randn(n, generator=g, dtype=F64)).float().to(F64), None
+    wq, wk = (1.0 + 0.2 * torch.randn(q, generator=g, dtype=F64)).float().to(F64), None
     ranges = [(0, dev(wq.float()), q - 2, EPS)]
     if k:
         wk = (1.0 + 0.2 * torch.randn(k, generator=g, dtype=F64)).float().to(F64)
