@@ -90,7 +90,7 @@ __device__ __forceinline__ float2 block_sum2(float a, float b, float* scratch /*
 // then every entry leaves scaled (entries outside the ranges, or all of them when there is no range, leave as
 // they are).  C, ld, out_ld, col0 and the ranges' borders are multiples of four.
 template <typename T, int NT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 6)
 causal_conv_norm_vec_kernel(const T* __restrict__ in, T* __restrict__ out, long long ld, long long out_ld, int col0,
                             int C, const float* __restrict__ taps, const float* __restrict__ state,
                             long long slot_stride, const int* __restrict__ tok_seg, const int* __restrict__ seg_start,

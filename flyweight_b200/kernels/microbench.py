@@ -6,6 +6,7 @@
     python -m flyweight_b200.kernels.microbench attention-prefill --tokens 2048
     python -m flyweight_b200.kernels.microbench shortconv --tokens 2048
     python -m flyweight_b200.kernels.microbench qk-norm-rope --tokens 2048
+    python -m flyweight_b200.kernels.microbench causal-conv --tokens 16384
     python -m flyweight_b200.kernels.microbench sample --rows 8 --top-k 40
 
 It is what the ncu summaries under ``profiles/`` were captured from (small cases of the same
@@ -167,6 +168,37 @@ def run_shortconv(args) -> dict:
             "gb_s": T * H * 2 * 4 / us / 1e3}
 
 
+def run_causal_conv(args) -> dict:
+    """The convolution on q|k|v rows with the norm over q and over k in the same launch (``--no-norm``: the
+    convolution alone), rows larger than L2 by default, a buffer larger than L2 written between launches."""
+    from ..engine import Segment, StepBatch
+    from . import mixing
+    T, q, kv, taps = args.tokens, args.q_channels, args.kv_channels, args.taps
+    C = q + 2 * kv
+    dtype = torch.bfloat16 if args.bf16 else torch.float32
+    rows = torch.randn(T, C + args.gate_columns, device="cuda").to(dtype)
+    w = torch.randn(C, taps, device="cuda")
+    state = torch.zeros(2, taps - 1, C, device="cuda") if taps > 1 else None
+    batch = StepBatch([Segment("a", 0, 0, [0] * (T // 2), []), Segment("b", 1, 5, [0] * (T - T // 2), [])],
+                      [[[0], [1]]], torch.device("cuda", 0))
+    ranges = None if args.no_norm else [(0, torch.ones(q, device="cuda"), q, 1e-5), (q, torch.ones(kv, device="cuda"), kv, 1e-5)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        mixing.causal_conv(rows, w, state, batch, norm_ranges=ranges)
+    times = []
+    for _ in range(args.repeat):
+        flush.zero_()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        mixing.causal_conv(rows, w, state, batch, norm_ranges=ranges)
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop) * 1e3)
+    us = sorted(times)[len(times) // 2]
+    return {"kernel": "causal_conv" + ("" if args.no_norm else "+norm"), "tokens": T, "channels": C, "taps": taps,
+            "dtype": str(dtype).split(".")[-1], "us": us, "gb_s": 2 * T * C * rows.element_size() / us / 1e3}
+
+
 def run_delta_rule(args) -> dict:
     """The gated delta rule's two kernels (prepare; scan) over ``batch`` segments of ``tokens`` tokens."""
     from ..engine.batch import Segment, StepBatch
@@ -323,6 +355,14 @@ def main(argv=None) -> int:
     conv.add_argument("--tokens", type=int, default=2048)
     conv.add_argument("--hidden", type=int, default=2048)
     conv.add_argument("--taps", type=int, default=3)
+    cconv = sub.add_parser("causal-conv")
+    cconv.add_argument("--tokens", type=int, default=16384)
+    cconv.add_argument("--q-channels", type=int, default=2048)
+    cconv.add_argument("--kv-channels", type=int, default=512)
+    cconv.add_argument("--taps", type=int, default=3)
+    cconv.add_argument("--gate-columns", type=int, default=32, help="columns behind q|k|v that the rows carry along")
+    cconv.add_argument("--bf16", action="store_true")
+    cconv.add_argument("--no-norm", action="store_true")
     rope = sub.add_parser("qk-norm-rope")
     rope.add_argument("--tokens", type=int, default=2048)
     rope.add_argument("--heads", type=int, default=32)
@@ -357,6 +397,7 @@ def main(argv=None) -> int:
     args = parser.parse_args(argv)
     runner = {"gemm": run_gemm, "attention-decode": run_attention_decode,
               "attention-prefill": run_attention_prefill, "shortconv": run_shortconv,
+              "causal-conv": run_causal_conv,
               "qk-norm-rope": run_qk_norm_rope, "sample": run_sample, "delta-rule": run_delta_rule,
               "linear-attention": run_linear_attention}[args.kernel]
     print(json.dumps(runner(args)))
