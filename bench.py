@@ -137,7 +137,7 @@ def fobatar_like(lfm2: dict, ff: int) -> dict:
                      "mask": {"size": 1024}, "rot": {"base": 1000000.0, "dims": 64, "scaling": ramp}}
             layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
     return {"architecture": "Fobatar", "vocab": lfm2["vocab_size"], "width": width, "norm": {"eps": 1e-5},
-            "embedding": {"scale": 1.0}, "residual_mult": 0.5, "loop": {"start": 2, "stop": 4, "times": 2},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.6, "loop": {"start": 2, "stop": 4, "times": 2},
             "layers": layers}
 
 
